@@ -839,3 +839,88 @@ HB_EXPORT int hb_sigmoid_gate(void* x, int is_bf16, int x_stride, const float* g
     }
     return launch_status();
 }
+
+// ---------------------------------------------------------------- residual add of up to two sublayer outputs + RMS norm in groups
+// Output row r reads source row s = rows ? rows[r] : r:  v = h[s] + (d1[s] + d2[s]) (either may be absent; the two outputs are added
+// to one another first, then to the stream), written back into h with `write_h`.  The row is cut into `groups` equal consecutive parts
+// and each is divided by its own sqrt(mean(part^2) + eps); the whole is multiplied by the weight.  A warp owns a part's sum at a time
+// (lanes stride over the part, then a butterfly), so the sums have one shape whatever the launch.  Everything is float until the one
+// rounding of the result.  The row's sums are kept in shared memory (at most 64 groups).
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) add_group_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ d1, const TD* __restrict__ d2,
+                                                                const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows,
+                                                                int hidden, int groups, float eps, int write_h) {
+    __shared__ float inv[64];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* hrow = h + (size_t)s * hidden;
+    const TD* a = d1 ? d1 + (size_t)s * hidden : nullptr;
+    const TD* b = d2 ? d2 + (size_t)s * hidden : nullptr;
+    const int part = hidden / groups, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int g = warp; g < groups; g += warps) {
+        float sum = 0.f;
+        for (int i = g * part + lane; i < (g + 1) * part; i += 32) {
+            float v = hrow[i];
+            if (a && b) v += to_float(a[i]) + to_float(b[i]);
+            else if (a) v += to_float(a[i]);
+            else if (b) v += to_float(b[i]);
+            if (write_h && (a || b)) hrow[i] = v;
+            sum = fmaf(v, v, sum);
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) inv[g] = 1.0f / sqrtf(sum / (float)part + eps);
+    }
+    __syncthreads();
+    TO* orow = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = hrow[i];
+        if (!write_h) {
+            if (a && b) v += to_float(a[i]) + to_float(b[i]);
+            else if (a) v += to_float(a[i]);
+            else if (b) v += to_float(b[i]);
+        }
+        orow[i] = from_float<TO>(v * inv[i / part] * weight[i]);
+    }
+}
+
+HB_EXPORT int hb_add_group_rmsnorm(float* h, const void* d1, const void* d2, int delta_is_bf16, const float* weight, void* out, int out_is_bf16,
+                                   const int* rows, int n_rows, int hidden, int groups, float eps, int write_h, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (hidden <= 0 || groups <= 0 || groups > 64 || hidden % groups) return HB_UNSUPPORTED_SIZE;
+    const int threads = groups >= 8 ? 256 : (groups * 32 < 128 ? 128 : groups * 32);
+#define HB_GROUP_NORM(TD, TO) add_group_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h)
+    if (delta_is_bf16 && out_is_bf16) HB_GROUP_NORM(__nv_bfloat16, __nv_bfloat16);
+    else if (delta_is_bf16) HB_GROUP_NORM(__nv_bfloat16, float);
+    else if (out_is_bf16) HB_GROUP_NORM(float, __nv_bfloat16);
+    else HB_GROUP_NORM(float, float);
+#undef HB_GROUP_NORM
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- a gated unit whose gate and value are clamped
+// in: [tokens, 2*inter], all gate columns first.  g = min(gate, limit); u = clamp(up, -limit, limit);
+// out[t, i] = g * sigmoid(slope * g) * (u + 1), in float, rounded once.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, float limit, float slope) {
+    const int t = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inter; i += gridDim.x * blockDim.x) {
+        const size_t at = (size_t)t * 2 * inter + i;
+        const float g = fminf(to_float(gate_up[at]), limit);
+        const float u = fminf(fmaxf(to_float(gate_up[at + inter]), -limit), limit);
+        out[(size_t)t * inter + i] = from_float<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+    }
+}
+
+HB_EXPORT int hb_clamped_glu(const void* gate_up, void* out, int is_bf16, int tokens, int inter, float limit, float slope, cudaStream_t stream) {
+    if (tokens <= 0 || inter <= 0) return 0;
+    for (int first = 0; first < tokens; first += 65535) {
+        const int count = tokens - first < 65535 ? tokens - first : 65535;
+        const int across = (inter + 255) / 256;
+        const dim3 grid(across < 16 ? across : 16, count);
+        if (is_bf16)
+            clamped_glu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up + (size_t)first * 2 * inter, (__nv_bfloat16*)out + (size_t)first * inter, inter, limit, slope);
+        else
+            clamped_glu_kernel<<<grid, 256, 0, stream>>>((const float*)gate_up + (size_t)first * 2 * inter, (float*)out + (size_t)first * inter, inter, limit, slope);
+    }
+    return launch_status();
+}

@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_whole, float eps, const float* __restrict__ inv_freq,
     int rot_dims, int rot_half, const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride,
     TO* __restrict__ k_cache, TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride,
-    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps,
+    int* status) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, head = blockIdx.y;  // q heads, then k heads, then v heads
     const int pos = positions[t];
@@ -171,8 +172,14 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
         const int vh = head - q_heads - kv_heads;
         const float* p = row + v_off + (size_t)vh * v_dim;
         TO* dst = page >= 0 ? v_cache + (size_t)page * page_stride + (size_t)vh * head_stride + (size_t)slot * token_stride : nullptr;
+        float inv = 1.f;
+        if (v_unit_eps >= 0.f) {  // the value head leaves with a root mean square of one
+            float sum = 0.f;
+            for (int i = threadIdx.x; i < v_dim; i += THREADS) sum = fmaf(p[i], p[i], sum);
+            inv = 1.0f / sqrtf(block_sum(sum, scratch) / (float)v_dim + v_unit_eps);
+        }
         if (!dst) return;
-        for (int i = threadIdx.x; i < v_dim; i += THREADS) dst[i] = from_float<TO>(p[i]);
+        for (int i = threadIdx.x; i < v_dim; i += THREADS) dst[i] = from_float<TO>(p[i] * inv);
     }
 }
 }  // namespace
@@ -213,7 +220,7 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims, int rot_half,
     const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride, TO* __restrict__ k_cache,
     TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride, const int* __restrict__ block_table, int table_width,
-    const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps, int* status) {
     __shared__ float scratch[32];
     __shared__ float cs[MAX_PAIRS], sn[MAX_PAIRS];
     const int t = blockIdx.x;
@@ -254,7 +261,17 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
         TO* key_page = page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)slot * token_stride : nullptr;
         prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
                                    [&](int head) { return key_page ? key_page + (size_t)head * head_stride : nullptr; });
-        if (page >= 0) {
+        if (page >= 0 && v_unit_eps >= 0.f) {  // every value head leaves with a root mean square of one: a warp per head
+            TO* value_page = v_cache + (size_t)page * page_stride + (size_t)slot * token_stride;
+            const int lane = threadIdx.x & 31;
+            for (int head = k_first + (threadIdx.x >> 5); head < k_first + k_count; head += TOKEN_THREADS / 32) {
+                const float* p = row + v_off + (size_t)head * v_dim;
+                float sum = 0.f;
+                for (int d = lane; d < v_dim; d += 32) sum = fmaf(p[d], p[d], sum);
+                const float inv = 1.0f / sqrtf(warp_sum(sum) / (float)v_dim + v_unit_eps);
+                for (int d = lane; d < v_dim; d += 32) value_page[(size_t)head * head_stride + d] = from_float<TO>(p[d] * inv);
+            }
+        } else if (page >= 0) {
             TO* value_page = v_cache + (size_t)page * page_stride + (size_t)slot * token_stride;
             for (int item = threadIdx.x; item < k_count * v_dim; item += TOKEN_THREADS) {
                 const int head = k_first + item / v_dim, d = item % v_dim;
@@ -274,8 +291,8 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                     int v_dim, const float* q_norm, const float* k_norm, int norm_whole, float eps, const float* inv_freq, int rot_dims,
                                     int rot_half, const int* positions, float k_scale, void* q_out, int q_out_stride, void* k_out, int k_out_stride,
                                     int out_is_bf16, void* k_cache, void* v_cache, long long page_stride, long long head_stride, int token_stride,
-                                    const int* block_table, int table_width, const int* token_row, int page_size, int pages, int* status,
-                                    cudaStream_t stream) {
+                                    const int* block_table, int table_width, const int* token_row, int page_size, int pages, float v_unit_eps,
+                                    int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1) || !q_out || (!k_cache && !k_out)) return HB_UNSUPPORTED_SIZE;
     const int heads = q_heads + kv_heads + (k_cache ? kv_heads : 0);
@@ -290,13 +307,13 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                              (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                              (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width,
-                                                                             token_row, page_size, pages, status);
+                                                                             token_row, page_size, pages, v_unit_eps, status);
         else
             heads_prepare_token_kernel<<<token_grid, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                              (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                              (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size,
-                                                                             pages, status);
+                                                                             pages, v_unit_eps, status);
         return launch_status();
     }
     const dim3 grid(tokens, heads);
@@ -305,12 +322,114 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                                                 eps, inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                 (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                 (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width, token_row,
-                                                                page_size, pages, status);
+                                                                page_size, pages, v_unit_eps, status);
     else
         heads_prepare_wide_kernel<<<grid, THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, norm_whole,
                                                                 eps, inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                 (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                 (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size, pages,
-                                                                status);
+                                                                v_unit_eps, status);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- attention over a latent: what lies between its products
+// A token's down-projections arrive as one float row: the query latent (q_rank entries at q_off) and, at kv_off, the key/value
+// latent (kv_rank entries) followed by one key part of rot_dim entries that every head shares.  Both latents pass an RMS norm
+// with a weight per entry; the first rot_dims entries of the shared key part are rotated in adjacent pairs, the rest pass as they
+// are.  The query latent goes to a dense buffer (the next product's input); latent and key part go to the token's place in its
+// page, the latent first: one record of kv_rank + rot_dim per token.  One block per token; sums, angles and products are float.
+namespace {
+template <typename TO>
+__global__ void __launch_bounds__(TOKEN_THREADS) latent_prepare_kernel(
+    const float* __restrict__ x, int stride, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot_dims,
+    const float* __restrict__ q_norm, const float* __restrict__ kv_norm, float eps, const float* __restrict__ inv_freq,
+    const int* __restrict__ positions, TO* __restrict__ cq_out, int cq_stride, TO* __restrict__ cache, size_t page_stride, int token_stride,
+    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const float* row = x + (size_t)t * stride;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += TOKEN_THREADS) sum = fmaf(row[q_off + i], row[q_off + i], sum);
+    const float inv_q = 1.0f / sqrtf(block_sum(sum, scratch) / (float)q_rank + eps);
+    sum = 0.f;
+    for (int i = threadIdx.x; i < kv_rank; i += TOKEN_THREADS) sum = fmaf(row[kv_off + i], row[kv_off + i], sum);
+    const float inv_c = 1.0f / sqrtf(block_sum(sum, scratch) / (float)kv_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += TOKEN_THREADS) cq_out[(size_t)t * cq_stride + i] = from_float<TO>(row[q_off + i] * inv_q * q_norm[i]);
+    const int block = pos / page_size;
+    int page = (pos >= 0 && block < table_width) ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+    if (page < 0 || page >= pages) {
+        if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+        return;
+    }
+    TO* dst = cache + (size_t)page * page_stride + (size_t)(pos - block * page_size) * token_stride;
+    for (int i = threadIdx.x; i < kv_rank; i += TOKEN_THREADS) dst[i] = from_float<TO>(row[kv_off + i] * inv_c * kv_norm[i]);
+    const float* part = row + kv_off + kv_rank;
+    for (int i = threadIdx.x; i < rot_dims / 2; i += TOKEN_THREADS) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        const float u = part[2 * i], v = part[2 * i + 1];
+        dst[kv_rank + 2 * i] = from_float<TO>(u * c - v * s);
+        dst[kv_rank + 2 * i + 1] = from_float<TO>(v * c + u * s);
+    }
+    for (int i = rot_dims + threadIdx.x; i < rot_dim; i += TOKEN_THREADS) dst[kv_rank + i] = from_float<TO>(part[i]);
+}
+
+// The query that meets the cached records: per head, the query's unrotated part already carried into the latent's space
+// (q_lat [head, token, kv_rank] float, the product of that part with the head's key matrix) followed by the head's rotated part,
+// which is taken from the up-projected queries q [token, head, dim + rot_dim] and rotated here.  One block per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(THREADS) latent_query_kernel(const T* __restrict__ q, int q_stride, int dim, int rot_dim, int rot_dims,
+                                                                const float* __restrict__ q_lat, size_t lat_head_stride, int lat_token_stride,
+                                                                int kv_rank, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                                                T* __restrict__ out, int out_stride) {
+    const int t = blockIdx.x, head = blockIdx.y;
+    const int pos = positions[t];
+    T* dst = out + (size_t)t * out_stride + (size_t)head * (kv_rank + rot_dim);
+    const float* lat = q_lat + (size_t)head * lat_head_stride + (size_t)t * lat_token_stride;
+    for (int i = threadIdx.x; i < kv_rank; i += THREADS) dst[i] = from_float<T>(lat[i]);
+    const T* part = q + (size_t)t * q_stride + (size_t)head * (dim + rot_dim) + dim;
+    for (int i = threadIdx.x; i < rot_dims / 2; i += THREADS) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        const float u = to_float(part[2 * i]), v = to_float(part[2 * i + 1]);
+        dst[kv_rank + 2 * i] = from_float<T>(u * c - v * s);
+        dst[kv_rank + 2 * i + 1] = from_float<T>(v * c + u * s);
+    }
+    for (int i = rot_dims + threadIdx.x; i < rot_dim; i += THREADS) dst[kv_rank + i] = part[i];
+}
+}  // namespace
+
+HB_EXPORT int hb_latent_prepare(const float* x, int tokens, int stride, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot_dims,
+                                const float* q_norm, const float* kv_norm, float eps, const float* inv_freq, const int* positions, void* cq_out,
+                                int cq_stride, int out_is_bf16, void* cache, long long page_stride, int token_stride, const int* block_table,
+                                int table_width, const int* token_row, int page_size, int pages, int* status, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (q_rank <= 0 || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1) || page_size <= 0) return HB_UNSUPPORTED_SIZE;
+    if (!q_norm || !kv_norm || !cq_out || !cache || (rot_dims && !inv_freq)) return HB_BAD_ARGUMENT;
+    if (out_is_bf16)
+        latent_prepare_kernel<<<tokens, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, eps, inv_freq,
+                                                                    positions, (__nv_bfloat16*)cq_out, cq_stride, (__nv_bfloat16*)cache, (size_t)page_stride,
+                                                                    token_stride, block_table, table_width, token_row, page_size, pages, status);
+    else
+        latent_prepare_kernel<<<tokens, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, eps, inv_freq,
+                                                                    positions, (float*)cq_out, cq_stride, (float*)cache, (size_t)page_stride, token_stride,
+                                                                    block_table, table_width, token_row, page_size, pages, status);
+    return launch_status();
+}
+
+HB_EXPORT int hb_latent_query(const void* q, int is_bf16, int tokens, int q_stride, int heads, int dim, int rot_dim, int rot_dims, const float* q_lat,
+                              long long lat_head_stride, int lat_token_stride, int kv_rank, const float* inv_freq, const int* positions, void* out,
+                              int out_stride, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || dim <= 0 || kv_rank <= 0 || rot_dim < 0 || rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1)) return HB_UNSUPPORTED_SIZE;
+    if (rot_dims && !inv_freq) return HB_BAD_ARGUMENT;
+    const dim3 grid(tokens, heads);
+    if (is_bf16)
+        latent_query_kernel<<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)q, q_stride, dim, rot_dim, rot_dims, q_lat, (size_t)lat_head_stride,
+                                                          lat_token_stride, kv_rank, inv_freq, positions, (__nv_bfloat16*)out, out_stride);
+    else
+        latent_query_kernel<<<grid, THREADS, 0, stream>>>((const float*)q, q_stride, dim, rot_dim, rot_dims, q_lat, (size_t)lat_head_stride, lat_token_stride,
+                                                          kv_rank, inv_freq, positions, (float*)out, out_stride);
     return launch_status();
 }

@@ -10,6 +10,8 @@
 //     delta rule:   S <- a S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q
 //     state space:  S <- a S + k (b v)^T;                           o = S^T q + D v
 //     retention:    S <- a S + k v^T  (a fixed per head);           o = S^T q
+//     wkv:          o = S^T q + (sum_i u_i k_i q_i) v;  S <- diag(w) S + k v^T,  w_i = exp(-exp(x_i + w0_i))
+//                   (a decay per key entry computed from the token, and a bonus u that only the current token gets)
 // Column j of S (one value dimension) never meets another column, so the work is cut by columns:
 // eight lanes share a column, each holding n / 8 of its entries in registers (groups of four
 // consecutive entries, stored as S^T so that they are one 16-byte access), and a block of 128
@@ -21,7 +23,7 @@
 
 namespace {
 constexpr int SCAN_THREADS = 128;
-enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1, MODE_RETENTION = 2 };
+enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1, MODE_RETENTION = 2, MODE_WKV = 3 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -63,12 +65,14 @@ __global__ void conv_state_update_kernel(const float* __restrict__ x, int x_stri
 
 // ---------------------------------------------------------------- the scan
 struct ScanArgs {
-    const float* conv;   // [tokens, conv_stride]: convolved and activated keys, queries and values
-    int conv_stride, k_off, q_off, v_off;
-    const float* proj;   // [tokens, proj_stride]: raw projections that give the decay and the step
+    const float* k;      // [tokens, k_stride]: keys (convolved and activated where the mixer has a convolution), group g at g * n
+    const float* q;      // [tokens, q_stride]: queries, likewise
+    const float* v;      // [tokens, v_stride]: values, head h at h * e
+    int k_stride, q_stride, v_stride;
+    const float* proj;   // [tokens, proj_stride]: raw projections that give the decay and the step (wkv: heads * n entries at decay_off)
     int proj_stride, decay_off, step_off;
-    const float* a_log;  // [heads]
-    const float* dt_bias;  // [heads]
+    const float* a_log;  // [heads] (wkv: w0 [heads * n])
+    const float* dt_bias;  // [heads] (wkv: the bonus u [heads * n])
     const float* skip;   // [heads] (state space: D)
     float* state;
     size_t slot_stride;
@@ -89,9 +93,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     // from shared memory once for all of them, and the columns' chains, which never meet, fill one another's waits (a prompt
     // gives the GPU fewer warps than it has schedulers, so nothing else would).
     constexpr int NP = NG * 4 * LPC, NPR = NP / 32, GROUPS = 128 / LPC, COLUMNS = GROUPS * CPT, VR = (COLUMNS + 31) / 32;
-    constexpr int CT = NP >= 256 ? 8 : 16, PER_WARP = CT / 4;
+    constexpr bool WKV = MODE == MODE_WKV;  // a third vector per token (its decays) passes through shared memory: shorter chunks
+    constexpr int CT = WKV ? (NP >= 256 ? 4 : (NP >= 128 ? 8 : 16)) : (NP >= 256 ? 8 : 16), PER_WARP = CT / 4;
     __shared__ __align__(16) float sk[2][CT][NP];
     __shared__ __align__(16) float sq[2][CT][NP];
+    __shared__ __align__(16) float sw[WKV ? 2 : 1][WKV ? CT : 1][WKV ? NP : 4];
     __shared__ float sv[2][CT][VR * 32], sdecay[2][CT], sstep[2][CT];
 
     const int row = blockIdx.z, head = blockIdx.y;
@@ -114,20 +120,28 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
             s[c][r][0] = v.x; s[c][r][1] = v.y; s[c][r][2] = v.z; s[c][r][3] = v.w;
         }
     }
-    const float a_rate = MODE == MODE_RETENTION ? 0.f : expf(a.a_log[head]);
+    const float a_rate = (MODE == MODE_RETENTION || WKV) ? 0.f : expf(a.a_log[head]);
     const float fixed_decay = MODE == MODE_RETENTION ? a.a_log[head] : 0.f;
-    const float bias = MODE == MODE_RETENTION ? 0.f : a.dt_bias[head];
+    const float bias = (MODE == MODE_RETENTION || WKV) ? 0.f : a.dt_bias[head];
+    float w0[NPR], bonus[NPR];  // wkv: this lane's entries of the head's decay offset and bonus
+#pragma unroll
+    for (int r = 0; r < NPR; ++r) {
+        const int index = lane + 32 * r;
+        w0[r] = (WKV && index < a.n) ? a.a_log[(size_t)head * a.n + index] : 0.f;
+        bonus[r] = (WKV && index < a.n) ? a.dt_bias[(size_t)head * a.n + index] : 0.f;
+    }
     const float skip = MODE == MODE_STATE_SPACE ? a.skip[head] : 0.f;
 
-    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP][VR], pdecay[PER_WARP], pstep[PER_WARP];
+    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP][VR], pdecay[PER_WARP], pstep[PER_WARP], pw[PER_WARP][WKV ? NPR : 1];
     auto prefetch = [&](int first) {
 #pragma unroll
         for (int i = 0; i < PER_WARP; ++i) {
             const int t = first + warp + 4 * i;
             const bool live = t < t1;
-            const float* c = a.conv + (size_t)(live ? t : t0) * a.conv_stride;
-            const float* k = c + a.k_off + (size_t)group * a.n;
-            const float* q = c + a.q_off + (size_t)group * a.n;
+            const size_t at = (size_t)(live ? t : t0);
+            const float* k = a.k + at * a.k_stride + (size_t)group * a.n;
+            const float* q = a.q + at * a.q_stride + (size_t)group * a.n;
+            const float* vals = a.v + at * a.v_stride + (size_t)head * a.e;
 #pragma unroll
             for (int r = 0; r < NPR; ++r) {
                 const int index = lane + 32 * r;
@@ -137,10 +151,17 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
 #pragma unroll
             for (int r = 0; r < VR; ++r) {
                 const int column = lane + 32 * r;
-                pv[i][r] = (live && column < COLUMNS && col0 + column < a.e) ? c[a.v_off + (size_t)head * a.e + col0 + column] : 0.f;
+                pv[i][r] = (live && column < COLUMNS && col0 + column < a.e) ? vals[col0 + column] : 0.f;
             }
-            const float* p = a.proj + (size_t)(live ? t : t0) * a.proj_stride;
-            pdecay[i] = (live && MODE != MODE_RETENTION) ? p[a.decay_off + head] : 0.f;
+            const float* p = a.proj + at * a.proj_stride;
+            if (WKV) {
+#pragma unroll
+                for (int r = 0; r < NPR; ++r) {
+                    const int index = lane + 32 * r;
+                    pw[i][r] = (live && index < a.n) ? p[a.decay_off + (size_t)head * a.n + index] : 0.f;
+                }
+            }
+            pdecay[i] = (live && MODE != MODE_RETENTION && !WKV) ? p[a.decay_off + head] : 0.f;
             pstep[i] = (live && MODE == MODE_DELTA) ? p[a.step_off + head] : 0.f;
         }
     };
@@ -163,9 +184,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
             }
 #pragma unroll
             for (int r = 0; r < VR; ++r) sv[buffer][j][lane + 32 * r] = pv[i][r];
+            float bonus_dot = 0.f;
+            if (WKV) {  // the entries' decays, and what the bonus adds to the token's own value: sum_i u_i k_i q_i
+#pragma unroll
+                for (int r = 0; r < NPR; ++r) {
+                    sw[buffer][j][lane + 32 * r] = expf(-expf(pw[i][r] + w0[r]));
+                    bonus_dot = fmaf(bonus[r] * pk[i][r], pq[i][r], bonus_dot);
+                }
+                bonus_dot = warp_sum(bonus_dot);
+            }
             if (lane == 0) {
                 float decay, step;
-                if (MODE == MODE_DELTA) {
+                if (WKV) {
+                    decay = 1.f;
+                    step = bonus_dot;
+                } else if (MODE == MODE_DELTA) {
                     decay = expf(-a_rate * softplus_f(pdecay[i] + bias));
                     step = 1.0f / (1.0f + expf(-pstep[i]));
                 } else if (MODE == MODE_RETENTION) {  // the head's decay is a constant of the model; keys enter as they are
@@ -202,6 +235,36 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
             float cv[CPT], u[CPT], o[CPT];
 #pragma unroll
             for (int c = 0; c < CPT; ++c) cv[c] = sv[buffer][j][cw + GROUPS * c];
+            if (WKV) {
+                float cd[NG][4];
+#pragma unroll
+                for (int r = 0; r < NG; ++r) {
+                    const float4 d4 = *reinterpret_cast<const float4*>(&sw[buffer][j][4 * (LPC * r + l)]);
+                    cd[r][0] = d4.x; cd[r][1] = d4.y; cd[r][2] = d4.z; cd[r][3] = d4.w;
+                }
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {  // the query meets the state as the token found it; then the state fades and takes k v^T
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int r = 0; r < NG; ++r)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            part[i] = fmaf(s[c][r][i], cq[r][i], part[i]);
+                            s[c][r][i] = fmaf(s[c][r][i], cd[r][i], ck[r][i] * cv[c]);
+                        }
+                    o[c] = (part[0] + part[1]) + (part[2] + part[3]);
+                }
+#pragma unroll
+                for (int offset = 1; offset < LPC; offset <<= 1)
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) o[c] += __shfl_xor_sync(0xffffffffu, o[c], offset);
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    const int col = col0 + cw + GROUPS * c;
+                    if (l == 0 && col < a.e && a.out) a.out[((size_t)(first + j) * a.heads + head) * a.e + col] = fmaf(step, cv[c], o[c]);
+                }
+                continue;
+            }
             if (MODE == MODE_DELTA) {
                 float dot[CPT];
 #pragma unroll
@@ -275,7 +338,7 @@ int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
     // reduction to the chain, rose from 783 / 939 us to 960 with two and 1,071 with four; eight decoded tokens gain a fifth either way.
     constexpr int LANES = 8;
     const int per_lane = (a.n_padded + 4 * LANES - 1) / (4 * LANES);  // groups of four entries per lane
-    constexpr int PER_THREAD = MODE == MODE_DELTA ? 1 : 2;
+    constexpr int PER_THREAD = MODE == MODE_DELTA ? 1 : 2;  // wkv: two, like the other recurrences whose columns add no reduction to the chain
     const int columns = (128 / LANES) * PER_THREAD;
     const dim3 grid((a.e + columns - 1) / columns, a.heads, rows);
     if (per_lane <= 1) state_scan_kernel<1, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
@@ -376,12 +439,97 @@ HB_EXPORT int hb_state_scan(int mode, const float* conv, int conv_stride, int k_
     if (rows <= 0) return 0;
     if (n <= 0 || n > 256 || e <= 0 || heads <= 0 || groups <= 0 || heads % groups || rows > 65535 || heads > 65535) return HB_UNSUPPORTED_SIZE;
     if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15)) return HB_BAD_ARGUMENT;
-    ScanArgs a{conv, conv_stride, k_off, q_off, v_off, proj, proj_stride, decay_off, step_off, a_log, dt_bias, skip, state, (size_t)slot_stride,
-               state_off, slots, row_start, out, heads, groups, n, n_padded, e, q_scale};
+    ScanArgs a{conv + k_off, conv + q_off, conv + v_off, conv_stride, conv_stride, conv_stride, proj, proj_stride, decay_off, step_off, a_log, dt_bias, skip,
+               state, (size_t)slot_stride, state_off, slots, row_start, out, heads, groups, n, n_padded, e, q_scale};
     if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, rows, stream);
     if (mode == MODE_STATE_SPACE) return launch_scan<MODE_STATE_SPACE>(a, rows, stream);
     if (mode == MODE_RETENTION) return launch_scan<MODE_RETENTION>(a, rows, stream);
     return HB_BAD_ARGUMENT;
+}
+
+// The wkv recurrence: keys, queries and values from three float matrices of their own (heads * n, heads * n and heads * e columns), the
+// decays' pre-activations x [tokens, heads * n] (w = exp(-exp(x + w0))), w0 and the bonus u [heads * n].  The state as in hb_state_scan.
+HB_EXPORT int hb_wkv_scan(const float* k, int k_stride, const float* q, int q_stride, const float* v, int v_stride, const float* x, int x_stride, int x_off,
+                          const float* w0, const float* bonus, float* state, long long slot_stride, int state_off, const int* slots, const int* row_start,
+                          float* out, int rows, int heads, int n, int n_padded, int e, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0 || n > 256 || e <= 0 || heads <= 0 || rows > 65535 || heads > 65535) return HB_UNSUPPORTED_SIZE;
+    if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15) || !w0 || !bonus) return HB_BAD_ARGUMENT;
+    ScanArgs a{k, q, v, k_stride, q_stride, v_stride, x, x_stride, x_off, 0, w0, bonus, nullptr, state, (size_t)slot_stride, state_off, slots, row_start, out,
+               heads, heads, n, n_padded, e, 1.f};
+    return launch_scan<MODE_WKV>(a, rows, stream);
+}
+
+// ---------------------------------------------------------------- token shift
+// A mixer that reads every token beside the one before it: input s of the mixer is h + (h' - h) * mu_s, h' being the row of the token
+// before (of the same request; its last token of the step before, kept in the request's slot, for the first token of a step; zeros
+// at the start of a request, which is what a fresh slot holds).  out [n_mix, tokens, hidden]: a dense matrix per input.  The
+// arithmetic is float, rounded once.  hb_token_shift_keep then stores every row's last token (as floats) for the next step.
+namespace {
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ mu, int n_mix, const float* __restrict__ state,
+                                       size_t slot_stride, int state_off, const int* __restrict__ slots, const int* __restrict__ token_row,
+                                       const int* __restrict__ row_start, T* __restrict__ out, int tokens, int hidden) {
+    const int t = blockIdx.x;
+    const int row = token_row[t];
+    const bool first = t == row_start[row];
+    const T* now = x + (size_t)t * x_stride;
+    const T* before = x + (size_t)(t - 1) * x_stride;
+    const float* kept = state + (size_t)slots[row] * slot_stride + state_off;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float h = to_float(now[i]);
+        const float d = (first ? kept[i] : to_float(before[i])) - h;
+        for (int m = 0; m < n_mix; ++m) out[((size_t)m * tokens + t) * hidden + i] = from_float<T>(fmaf(d, mu[(size_t)m * hidden + i], h));
+    }
+}
+
+template <typename T>
+__global__ void token_shift_keep_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state, size_t slot_stride, int state_off,
+                                        const int* __restrict__ slots, const int* __restrict__ row_start, int hidden) {
+    const int row = blockIdx.x;
+    const int last = row_start[row + 1] - 1;
+    if (last < row_start[row]) return;
+    float* kept = state + (size_t)slots[row] * slot_stride + state_off;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) kept[i] = to_float(x[(size_t)last * x_stride + i]);
+}
+
+template <typename T>
+__global__ void tanh_rows_kernel(const float* __restrict__ x, T* __restrict__ out, long long count) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) out[i] = from_float<T>(tanhf(x[i]));
+}
+}  // namespace
+
+HB_EXPORT int hb_token_shift_mix(const void* x, int is_bf16, int x_stride, const float* mu, int n_mix, const float* state, long long slot_stride, int state_off,
+                                 const int* slots, const int* token_row, const int* row_start, void* out, int tokens, int hidden, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || n_mix <= 0) return HB_UNSUPPORTED_SIZE;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16)
+        token_shift_mix_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, mu, n_mix, state, (size_t)slot_stride, state_off, slots, token_row,
+                                                               row_start, (__nv_bfloat16*)out, tokens, hidden);
+    else
+        token_shift_mix_kernel<<<tokens, threads, 0, stream>>>((const float*)x, x_stride, mu, n_mix, state, (size_t)slot_stride, state_off, slots, token_row, row_start,
+                                                               (float*)out, tokens, hidden);
+    return launch_status();
+}
+
+HB_EXPORT int hb_token_shift_keep(const void* x, int is_bf16, int x_stride, float* state, long long slot_stride, int state_off, const int* slots,
+                                  const int* row_start, int rows, int hidden, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16) token_shift_keep_kernel<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, state, (size_t)slot_stride, state_off, slots, row_start, hidden);
+    else token_shift_keep_kernel<<<rows, 256, 0, stream>>>((const float*)x, x_stride, state, (size_t)slot_stride, state_off, slots, row_start, hidden);
+    return launch_status();
+}
+
+// out[i] = tanh(x[i]) of a dense float tensor, rounded once to the output's type.
+HB_EXPORT int hb_tanh_rows(const float* x, void* out, int out_is_bf16, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const long long wanted = (count + 255) / 256;
+    const int blocks = (int)(wanted < 2048 ? wanted : 2048);
+    if (out_is_bf16) tanh_rows_kernel<<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out, count);
+    else tanh_rows_kernel<<<blocks, 256, 0, stream>>>(x, (float*)out, count);
+    return launch_status();
 }
 
 HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gate, int gate_stride, int gate_off, const float* weight,

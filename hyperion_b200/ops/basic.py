@@ -236,13 +236,21 @@ def heads_prepare_(x: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, 
 def attention_general(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache: torch.Tensor, block_table: torch.Tensor,
                       token_row: torch.Tensor, positions: torch.Tensor, page_size: int, scale: float, softcap: float = 0.0, window: int = 0, *,
                       distance_bias: torch.Tensor | None = None, gate: torch.Tensor | None = None, gate_off: int = 0, out_scale: float = 1.0,
-                      out: torch.Tensor | None = None) -> torch.Tensor:
+                      out: torch.Tensor | None = None, head_scale: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
+                      sinks: torch.Tensor | None = None, chunk: int = 0, value_prefix: bool = False) -> torch.Tensor:
     """Causal attention of every token over its request's pages with keys of ``head_dim`` and values of ``v_dim``, a smooth
     cap on the scores (0 = none) and a window (0 = all keys); the cache in either arrangement of :func:`paged_strides`.
     ``distance_bias`` [heads, span] float: the score of a key ``n`` positions back takes ``distance_bias[head, min(n, span - 1)]``
     (after scale and cap).  ``gate`` [tokens, *] float: the result is multiplied by ``out_scale * sigmoid(gate[:, gate_off:][token, head * v_dim + i])``.
-    ``out``: a [tokens, >= heads * v_dim] view the result is written to."""
-    require_cuda(q, cache, block_table, token_row, positions, distance_bias, gate, out)
+    ``out``: a [tokens, >= heads * v_dim] view the result is written to.  ``head_scale`` [heads] float: a factor on the scaled score;
+    ``slopes`` [heads] float: ``slopes[head] * (query position - key position)`` is taken off the score; ``sinks`` [heads] float: one more
+    term ``exp(sinks[head])`` in the softmax's denominator, with no key and no value; ``chunk`` > 0: a query sees only the keys of its own
+    chunk of ``chunk`` positions (counted from position 0).  ``value_prefix``: the cache is [pages, kv_heads, page, head_dim] and a
+    token's value is the first ``v_dim`` entries of its key (attention over a latent)."""
+    require_cuda(q, cache, block_table, token_row, positions, distance_bias, gate, out, head_scale, slopes, sinks)
+    for t in (head_scale, slopes, sinks):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous()):
+            raise KernelError("attention: factors, slopes and sinks are dense float32 vectors with one entry per head")
     for t in (distance_bias, gate):
         if t is not None and (t.dtype != torch.float32 or t.stride(-1) != 1 or t.dim() != 2):
             raise KernelError("attention: the distance bias and the gate are float32 matrices with unit inner stride")
@@ -250,19 +258,25 @@ def attention_general(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
         raise KernelError("attention: the distance bias is a dense [heads, span] table")
     if q.dtype != cache.dtype or q.stride(-1) != 1:
         raise KernelError("attention: queries and cache must share their element type")
-    v_off, page_stride, head_stride, token_stride = paged_strides(cache, head_dim, v_dim)
+    if value_prefix:
+        if cache.dim() != 4 or cache.shape[1] != kv_heads or cache.shape[3] != head_dim or v_dim > head_dim or not cache.is_contiguous():
+            raise KernelError("attention: a cache of [pages, kv_heads, page, head_dim] whose values are the keys' first v_dim entries")
+        v_off, page_stride, head_stride, token_stride = 0, kv_heads * cache.shape[2] * head_dim, cache.shape[2] * head_dim, head_dim
+    else:
+        v_off, page_stride, head_stride, token_stride = paged_strides(cache, head_dim, v_dim)
     tokens = q.shape[0]
     if out is None:
         out = torch.empty((tokens, heads * v_dim), dtype=q.dtype, device=q.device)
     elif out.dtype != q.dtype or out.shape[0] != tokens or out.shape[1] < heads * v_dim or out.stride(1) != 1:
         raise KernelError("attention: the output is a [tokens, >= heads * v_dim] view of the queries' element type")
     v_cache = ctypes.c_void_p(cache.data_ptr() + v_off * cache.element_size())
-    check(library("attention_generic").hb_attention_biased(
+    check(library("attention_generic").hb_attention_extended(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), i32(is_bf16(q)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
         ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1]), ptr(token_row), ptr(positions), i32(tokens),
         i32(heads), i32(kv_heads), i32(head_dim), i32(v_dim), i32(page_size), i32(cache.shape[0]), f32(scale), f32(softcap or 0.0), i32(window or 0),
         ptr(distance_bias), i32(distance_bias.shape[1] if distance_bias is not None else 0), ptr(gate), i32(gate.stride(0) if gate is not None else 0),
-        i32(gate_off), f32(out_scale), ptr(status_word(q.device)), stream_ptr()), "attention_general")
+        i32(gate_off), f32(out_scale), ptr(head_scale), ptr(slopes), ptr(sinks), i32(chunk or 0), ptr(status_word(q.device)), stream_ptr()),
+        "attention_general")
     return out
 
 
@@ -270,12 +284,14 @@ def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_he
                        positions: torch.Tensor, *, q_out: torch.Tensor, k_out: torch.Tensor | None = None, q_norm: torch.Tensor | None = None,
                        k_norm: torch.Tensor | None = None, norm_whole: bool = False, eps: float = 0.0, inv_freq: torch.Tensor | None = None,
                        rot_dims: int = 0, rot_half: bool = False, k_scale: float = 1.0, cache: torch.Tensor | None = None,
-                       block_table: torch.Tensor | None = None, token_row: torch.Tensor | None = None, page_size: int = 0) -> None:
+                       block_table: torch.Tensor | None = None, token_row: torch.Tensor | None = None, page_size: int = 0,
+                       v_unit_eps: float | None = None) -> None:
     """Float projections ``x`` [tokens, *] with queries at column ``q_off``, keys at ``k_off``, values at ``v_off``: query/key
     norm (per head with one weight, or over the whole projection with a weight per column), rotation (adjacent pairs, or
     dimension i with i + rot_dims / 2), keys times ``k_scale``; queries to ``q_out`` [tokens, >= q_heads * head_dim], keys and
     values into ``cache`` (either arrangement of :func:`paged_strides`) or keys to ``k_out`` (values then stay where they are).
-    ``q_out`` and ``k_out`` may be float views of ``x`` itself."""
+    ``q_out`` and ``k_out`` may be float views of ``x`` itself.  ``v_unit_eps`` (with a cache): every value head is divided by
+    sqrt(mean(v^2) + v_unit_eps) before it is stored."""
     require_cuda(x, positions, q_out, k_out, q_norm, k_norm, inv_freq, cache, block_table, token_row)
     if x.dtype != torch.float32 or x.stride(-1) != 1 or q_out.stride(-1) != 1 or (k_out is not None and (k_out.stride(-1) != 1 or k_out.dtype != q_out.dtype)):
         raise KernelError("heads_prepare_wide: float32 projections and outputs with unit inner stride")
@@ -297,7 +313,84 @@ def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_he
         i32(1 if rot_half else 0), ptr(positions), f32(k_scale), ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
         i32(k_out.stride(0) if k_out is not None else 0), i32(is_bf16(q_out)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
         ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1] if block_table is not None else 0),
-        ptr(token_row), i32(page_size), i32(pages), ptr(status_word(x.device)), stream_ptr()), "heads_prepare_wide")
+        ptr(token_row), i32(page_size), i32(pages), f32(-1.0 if v_unit_eps is None else v_unit_eps), ptr(status_word(x.device)), stream_ptr()),
+        "heads_prepare_wide")
+
+
+def latent_prepare(x: torch.Tensor, q_off: int, q_rank: int, kv_off: int, kv_rank: int, rot_dim: int, q_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float,
+                   inv_freq: torch.Tensor | None, rot_dims: int, positions: torch.Tensor, out_dtype: torch.dtype, cache: torch.Tensor, block_table: torch.Tensor,
+                   token_row: torch.Tensor, page_size: int) -> torch.Tensor:
+    """Float down-projections ``x`` [tokens, *]: the query latent (``q_rank`` columns at ``q_off``) and the key/value latent (``kv_rank``
+    columns at ``kv_off``) followed by the shared key part of ``rot_dim`` columns.  Both latents pass an RMS norm with a weight per
+    entry; the key part's first ``rot_dims`` entries are rotated in adjacent pairs.  Returns the normed query latent [tokens, q_rank]
+    in ``out_dtype``; latent and key part go to ``cache`` [pages, 1, page, kv_rank + rot_dim]."""
+    require_cuda(x, q_norm, kv_norm, inv_freq, positions, cache, block_table, token_row)
+    if x.dtype != torch.float32 or x.stride(-1) != 1 or q_norm.dtype != torch.float32 or kv_norm.dtype != torch.float32:
+        raise KernelError("latent_prepare: float32 projections and norm weights")
+    if q_norm.numel() != q_rank or kv_norm.numel() != kv_rank or (rot_dims and (inv_freq is None or inv_freq.numel() < rot_dims // 2)):
+        raise KernelError("latent_prepare: a weight per latent entry and a frequency per rotated pair")
+    if cache.dtype != out_dtype or cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != kv_rank + rot_dim or not cache.is_contiguous():
+        raise KernelError("latent_prepare: a cache of [pages, 1, page, kv_rank + rot_dim] in the output's element type")
+    cq = torch.empty((x.shape[0], q_rank), dtype=out_dtype, device=x.device)
+    record = kv_rank + rot_dim
+    check(library("heads_prepare").hb_latent_prepare(
+        ptr(x), i32(x.shape[0]), i32(x.stride(0)), i32(q_off), i32(q_rank), i32(kv_off), i32(kv_rank), i32(rot_dim), i32(rot_dims), ptr(q_norm), ptr(kv_norm),
+        f32(eps), ptr(inv_freq), ptr(positions), ptr(cq), i32(cq.stride(0)), i32(is_bf16(cq)), ptr(cache), ctypes.c_longlong(cache.shape[2] * record),
+        i32(record), ptr(block_table), i32(block_table.shape[1]), ptr(token_row), i32(page_size), i32(cache.shape[0]), ptr(status_word(x.device)),
+        stream_ptr()), "latent_prepare")
+    return cq
+
+
+def latent_query(q: torch.Tensor, q_lat: torch.Tensor, heads: int, dim: int, rot_dim: int, inv_freq: torch.Tensor | None, rot_dims: int,
+                 positions: torch.Tensor) -> torch.Tensor:
+    """The queries that meet cached latent records: per head, ``q_lat`` [heads, tokens, kv_rank] float (the head's unrotated query part
+    carried into the latent's space) followed by the head's rotated part, taken from ``q`` [tokens, heads * (dim + rot_dim)] and
+    rotated in adjacent pairs over its first ``rot_dims`` entries.  Returns [tokens, heads * (kv_rank + rot_dim)] in ``q``'s type."""
+    require_cuda(q, q_lat, inv_freq, positions)
+    tokens = q.shape[0]
+    if q_lat.dtype != torch.float32 or q_lat.dim() != 3 or q_lat.shape[0] != heads or q_lat.shape[1] != tokens or q_lat.stride(2) != 1 or q.stride(-1) != 1:
+        raise KernelError("latent_query: q_lat is float32 [heads, tokens, kv_rank] with unit inner stride")
+    kv_rank = q_lat.shape[2]
+    out = torch.empty((tokens, heads * (kv_rank + rot_dim)), dtype=q.dtype, device=q.device)
+    check(library("heads_prepare").hb_latent_query(ptr(q), i32(is_bf16(q)), i32(tokens), i32(q.stride(0)), i32(heads), i32(dim), i32(rot_dim), i32(rot_dims),
+                                                   ptr(q_lat), ctypes.c_longlong(q_lat.stride(0)), i32(q_lat.stride(1)), i32(kv_rank), ptr(inv_freq),
+                                                   ptr(positions), ptr(out), i32(out.stride(0)), stream_ptr()), "latent_query")
+    return out
+
+
+def add_group_rmsnorm(h: torch.Tensor, first: torch.Tensor | None, second: torch.Tensor | None, weight: torch.Tensor, groups: int, eps: float,
+                      out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``h + (first + second)`` (either may be absent; the two are added to one another first), then the row is cut into ``groups``
+    equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps), the whole times ``weight``.  Without ``rows`` the sum is
+    written back into the float stream ``h``; with ``rows`` (int32 indices) only those rows are read and ``h`` is left alone."""
+    require_cuda(h, first, second, weight, rows)
+    if h.dtype != torch.float32 or weight.dtype != torch.float32 or not h.is_contiguous() or h.dim() != 2:
+        raise KernelError("add_group_rmsnorm: the residual stream and the norm weight are float32")
+    hidden = h.shape[1]
+    deltas = [d for d in (first, second) if d is not None]
+    for d in deltas:
+        if d.shape != h.shape or not d.is_contiguous() or d.dtype != deltas[0].dtype:
+            raise KernelError("add_group_rmsnorm: sublayer outputs are dense, of the stream's shape and of one element type")
+    if groups <= 0 or groups > 64 or hidden % groups:
+        raise KernelError(f"add_group_rmsnorm: {groups} groups do not divide {hidden} columns (at most 64 groups)")
+    n_rows = rows.numel() if rows is not None else h.shape[0]
+    out = torch.empty((n_rows, hidden), dtype=out_dtype, device=h.device)
+    check(library("elementwise").hb_add_group_rmsnorm(ptr(h), ptr(first), ptr(second), i32(is_bf16(deltas[0]) if deltas else 0), ptr(weight), ptr(out),
+                                                      i32(is_bf16(out)), ptr(rows), i32(n_rows), i32(hidden), i32(groups), f32(eps),
+                                                      i32(0 if rows is not None else 1), stream_ptr()), "add_group_rmsnorm")
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, limit: float, slope: float) -> torch.Tensor:
+    """[tokens, 2I] (all gate columns first) -> g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    require_cuda(gate_up)
+    if gate_up.dim() != 2 or not gate_up.is_contiguous() or gate_up.shape[1] % 2:
+        raise KernelError("clamped_glu: a dense [tokens, 2I] matrix")
+    tokens, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
+    check(library("elementwise").hb_clamped_glu(ptr(gate_up), ptr(out), i32(is_bf16(gate_up)), i32(tokens), i32(inter), f32(limit), f32(slope), stream_ptr()),
+          "clamped_glu")
+    return out
 
 
 def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor | None, eps_post: float, offset: torch.Tensor | None,

@@ -59,6 +59,58 @@ def state_scan(mode: int, conv: torch.Tensor, k_off: int, q_off: int, v_off: int
     return out
 
 
+def wkv_scan(k: torch.Tensor, q: torch.Tensor, v: torch.Tensor, x: torch.Tensor, x_off: int, w0: torch.Tensor, bonus: torch.Tensor, state: torch.Tensor,
+             state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, n: int, n_padded: int, e: int) -> torch.Tensor:
+    """The recurrence with a decay per key entry computed from the token and a bonus for the current token, per head:
+    o = S^T q + (sum_i u_i k_i q_i) v;  S <- diag(w) S + k v^T  with w = exp(-exp(x + w0)).  ``k``, ``q`` [tokens, heads * n] and ``v``
+    [tokens, heads * e] are float matrices of their own, ``x`` [tokens, *] holds the decays' pre-activations at column ``x_off``,
+    ``w0`` and ``bonus`` have heads * n entries.  Every row's tokens walk from and into its slot of ``state``.  Returns [tokens, heads * e]."""
+    require_cuda(k, q, v, x, w0, bonus, state, slots, row_start)
+    _floats(k, q, v, x, w0, bonus, state)
+    if w0.numel() != heads * n or bonus.numel() != heads * n or not w0.is_contiguous() or not bonus.is_contiguous():
+        raise KernelError("wkv_scan: the decay offset and the bonus have an entry per head and key entry")
+    out = torch.empty((k.shape[0], heads * e), dtype=torch.float32, device=k.device)
+    check(library("recurrent").hb_wkv_scan(ptr(k), i32(k.stride(0)), ptr(q), i32(q.stride(0)), ptr(v), i32(v.stride(0)), ptr(x), i32(x.stride(0)), i32(x_off),
+                                           ptr(w0), ptr(bonus), ptr(state), ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start),
+                                           ptr(out), i32(rows), i32(heads), i32(n), i32(n_padded), i32(e), stream_ptr()), "wkv_scan")
+    return out
+
+
+def token_shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_off: int, slots: torch.Tensor, token_row: torch.Tensor,
+                    row_start: torch.Tensor) -> torch.Tensor:
+    """[n_mix, tokens, hidden] in ``x``'s type: input s is ``x + (x' - x) * mu[s]``, x' the row of the token before of the same request
+    (from the request's slot of ``state`` at ``state_off`` for the first token of a step)."""
+    require_cuda(x, mu, state, slots, token_row, row_start)
+    _floats(mu, state)
+    tokens, hidden = x.shape
+    if x.stride(1) != 1 or mu.dim() != 2 or mu.shape[1] != hidden or not mu.is_contiguous():
+        raise KernelError("token_shift_mix: rows with unit inner stride and a dense [n_mix, hidden] table of mixing weights")
+    out = torch.empty((mu.shape[0], tokens, hidden), dtype=x.dtype, device=x.device)
+    check(library("recurrent").hb_token_shift_mix(ptr(x), i32(is_bf16(x)), i32(x.stride(0)), ptr(mu), i32(mu.shape[0]), ptr(state), ctypes.c_longlong(state.stride(0)),
+                                                  i32(state_off), ptr(slots), ptr(token_row), ptr(row_start), ptr(out), i32(tokens), i32(hidden), stream_ptr()),
+          "token_shift_mix")
+    return out
+
+
+def token_shift_keep(x: torch.Tensor, state: torch.Tensor, state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int) -> None:
+    """Every row's slot keeps the row's last token of ``x`` (as floats) for the next step (call after :func:`token_shift_mix`)."""
+    require_cuda(x, state, slots, row_start)
+    _floats(state)
+    check(library("recurrent").hb_token_shift_keep(ptr(x), i32(is_bf16(x)), i32(x.stride(0)), ptr(state), ctypes.c_longlong(state.stride(0)), i32(state_off),
+                                                   ptr(slots), ptr(row_start), i32(rows), i32(x.shape[1]), stream_ptr()), "token_shift_keep")
+
+
+def tanh_rows(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """tanh of a dense float tensor, rounded once to ``out_dtype``."""
+    require_cuda(x)
+    _floats(x)
+    if not x.is_contiguous():
+        raise KernelError("tanh_rows: a dense tensor")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(library("recurrent").hb_tanh_rows(ptr(x), ptr(out), i32(is_bf16(out)), ctypes.c_longlong(x.numel()), stream_ptr()), "tanh_rows")
+    return out
+
+
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight: torch.Tensor | None, group: int, gate_first: bool, eps: float,
                      out_dtype: torch.dtype, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
     """RMS norm of ``y`` [tokens, width] in groups of ``group`` columns, times ``weight`` (indexed by column modulo its length;

@@ -75,3 +75,21 @@ class SandwichNormBlock(Arrangement):
 
 
 register_arrangement("sandwich_norm", SandwichNormBlock)
+
+
+class SideBySideBlock(Arrangement):
+    """Mixer and feed-forward read the same normalised rows and their results are added to the stream together:
+    x = norm(h);  h <- h + (mixer(x) + feed_forward(x)).  One norm per layer (name ``input``).  What the two return travels
+    on as a :class:`SumOfTwo`; the next norm that reads the stream adds it in its own launch.  A layer without a
+    feed-forward adds the mixer's result alone."""
+
+    def forward(self, h, delta, step, cache, own_cache):
+        from .norm import SumOfTwo
+
+        x = self.norms["input"].forward(h, delta)
+        mixed = self.mixer.forward(x, step, cache, own_cache)
+        fed = self.feed_forward.forward(x, step) if self.feed_forward is not None else None
+        return h, SumOfTwo(mixed, fed)
+
+
+register_arrangement("side_by_side", SideBySideBlock)

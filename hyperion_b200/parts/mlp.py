@@ -90,3 +90,39 @@ class ActivatedMLP(FeedForward):
 
 
 register_feed_forward("activated_mlp", ActivatedMLP)
+
+
+class ClampedGLU(FeedForward):
+    """A gated feed-forward whose gate and value are clamped: g = min(gate(x), limit), u = clamp(up(x), -limit, limit),
+    down(g * sigmoid(slope * g) * (u + 1)), no biases.  gate and up are one [2I, H] matrix, the gate rows first.
+    Parameters: ``hidden_size``, ``intermediate_size``, ``limit``, ``gate_slope``, ``names`` (as for ``swiglu``)."""
+
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.limit = float(spec.params["limit"])
+        self.slope = float(spec.params.get("gate_slope", 1.0))
+        names = dict(spec.params.get("names") or {})
+        self.gate_name, self.up_name = names.get("gate", "gate_proj.weight"), names.get("up", "up_proj.weight")
+        self.down_name = names.get("down", "down_proj.weight")
+
+    def weights(self) -> dict[str, WeightSpec]:
+        return {self.gate_name: WeightSpec((self.inter, self.hidden)), self.up_name: WeightSpec((self.inter, self.hidden)),
+                self.down_name: WeightSpec((self.hidden, self.inter))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        pair = [tensors[self.gate_name], tensors[self.up_name]]
+        dtype = _common_dtype(pair)
+        self.w_gate_up = torch.cat([t.to(dtype) for t in pair], dim=0).contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def kernel_modules(self):
+        return [("elementwise", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+
+    def forward(self, x, step):
+        act = ops.clamped_glu(ops.linear(x, self.w_gate_up, None, self.dtype), self.limit, self.slope)
+        return ops.linear(act, self.w_down, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
+register_feed_forward("clamped_glu", ClampedGLU)

@@ -5,7 +5,8 @@ y = x * rsqrt(mean(x^2) + eps) * weight, the weight multiplying after the normal
 the residual stream (rmsnorm.cu:66-122).  The stream, the sum of squares and the products are float;
 the result is rounded once to the activation type.  Parameters: ``hidden_size``, ``eps``, ``weight_name`` (the tensor's
 name after the prefix, ``weight`` unless stated), ``one_plus`` (the tensor holds the weight's offset from one, which is added,
-in float, when it is loaded).
+in float, when it is loaded), ``groups`` (1 unless stated: the row is cut into that many equal consecutive parts and each is
+divided by its own sqrt(mean(part^2) + eps); the weight still has an entry per column).
 
 ``add_normed`` is the other placement of the same norm: h <- h + norm(y), for blocks that normalise what a sublayer
 returns instead of what it reads.
@@ -38,6 +39,25 @@ class NormedDelta:
         ops.norm_add_norm(h, y, self.norm.weight if y is not None else None, self.norm.eps if y is not None else 0.0, self.offset, None, 0.0, h.dtype)
 
 
+@dataclass
+class SumOfTwo:
+    """What two sublayers that read the same rows returned, still to be added to the stream: first to one another, then to the
+    stream.  The next norm that reads the stream does it in its own launch (``ops.add_group_rmsnorm``).  Either may be absent."""
+
+    first: Optional[torch.Tensor]
+    second: Optional[torch.Tensor]
+
+    def parts(self) -> tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        return tuple(d.tensor() if hasattr(d, "tensor") else d for d in (self.first, self.second))
+
+    def tensor(self) -> Optional[torch.Tensor]:
+        """The sum as one tensor, for a reader of the stream that adds a single delta."""
+        first, second = self.parts()
+        if first is None or second is None:
+            return first if second is None else second
+        return first.float() + second.float()
+
+
 def with_offset(h: torch.Tensor, delta, row: torch.Tensor):
     """The pending addition ``delta`` (None, a tensor, split-K pieces or a :class:`NormedDelta`) with ``row`` added after it."""
     if isinstance(delta, NormedDelta):
@@ -56,6 +76,9 @@ class RMSNorm(Norm):
         self.eps = float(spec.params["eps"])
         self.weight_name = str(spec.params.get("weight_name", "weight"))
         self.one_plus = bool(spec.params.get("one_plus", False))
+        self.groups = int(spec.params.get("groups", 1) or 1)
+        if self.groups < 1 or self.hidden % self.groups:
+            raise ValueError(f"{self.groups} groups do not divide a row of {self.hidden}")
         self.weight: Optional[torch.Tensor] = None
 
     def weights(self) -> dict[str, WeightSpec]:
@@ -70,6 +93,14 @@ class RMSNorm(Norm):
         return [("elementwise", {})]
 
     def forward(self, h, delta, rows=None):
+        if self.groups > 1 or isinstance(delta, SumOfTwo):
+            if isinstance(delta, NormedDelta):
+                delta.apply(h)
+                delta = None
+            first, second = delta.parts() if isinstance(delta, SumOfTwo) else (delta.tensor() if hasattr(delta, "tensor") else delta, None)
+            if first is not None and second is not None and first.dtype != second.dtype:
+                first, second = first.float(), second.float()
+            return ops.add_group_rmsnorm(h, first, second, self.weight, self.groups, self.eps, self.dtype, rows)
         if isinstance(delta, NormedDelta):
             y = delta.y.tensor() if hasattr(delta.y, "tensor") else delta.y
             return ops.norm_add_norm(h, y, delta.norm.weight if y is not None else None, delta.norm.eps if y is not None else 0.0, delta.offset,
@@ -78,6 +109,8 @@ class RMSNorm(Norm):
 
     def add_normed(self, h, y):
         """h <- h + norm(y) in the float stream; returns the new stream in the activation type (``h`` itself in float32)."""
+        if self.groups > 1:
+            raise ValueError("a norm in groups stands where a sublayer reads the stream, not on a sublayer's output")
         if hasattr(y, "tensor"):
             y = y.tensor()
         if self.dtype == torch.float32:

@@ -1,5 +1,5 @@
-"""Two mixers that keep a matrix-valued state per request instead of a cache of keys: the gated delta rule and
-the state-space mixer of Mamba-2.  Both are one in-projection, a short causal convolution with SiLU over some of
+"""Mixers that keep a matrix-valued state per request instead of a cache of keys.  The gated delta rule and
+the state-space mixer of Mamba-2 are both one in-projection, a short causal convolution with SiLU over some of
 its columns, a scan of the recurrence over each request's new tokens (``csrc/recurrent.cu``), a gated RMS norm,
 and an out-projection.  The in-projection's result, the convolution, the recurrence with its decays, step
 sizes and unit norms, the state and the norm are float32 in both precisions; only the matrix products take
@@ -28,6 +28,16 @@ a state of n entries per channel and step inputs of rank r:
     S[c, i] <- exp(dt_c A[c, i]) S[c, i] + dt_c x_c B_i  with A = -exp(A_log);  y_c = sum_i S[c, i] C_i + D_c x_c
     y <- y silu(z), then W_o.
 Parameters: ``hidden_size``, ``inner``, ``state``, ``dt_rank``, ``conv`` (taps).  Tensors: in, conv, conv.b, x, dt, dt.b, A_log, D, o.
+
+Time mixing with a decay per key entry (``wkv``), per head with key/query size n and value size n.  Every token is read beside
+the one before it: with x' the row of the token before (zeros at the start of a request), each of the five inputs s in (r, k, v, g, w)
+is x + (x' - x) * mu_s.
+    r, k, v = W_r in_r, W_k in_k, W_v in_v;  gate = silu(W_g in_g);  w = exp(-exp(W_w2 tanh(W_w1 in_w) + w0)), one per head and key entry
+    o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T   (the bonus u only ever meets the current token)
+    y = o / rms(o) per head, times norm, times gate, then W_o.
+The record holds the heads' matrices, then the last token's x.  Mixes, tanh, decays, the recurrence and the norm are float.
+Parameters: ``hidden_size``, ``heads``, ``head_dim``, ``decay_rank`` (what random weights get; a checkpoint's tensors decide), ``eps``.
+Tensors: mu.r, mu.k, mu.v, mu.g, mu.w, r, k, v, g, w1, w2, w0, u, norm, o.
 """
 from __future__ import annotations
 
@@ -221,6 +231,59 @@ class SelectiveScanMixer(Mixer):
         return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 
+class WkvMixer(Mixer):
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        p = spec.params
+        self.hidden, self.heads, self.n = int(p["hidden_size"]), int(p["heads"]), int(p["head_dim"])
+        self.decay_rank, self.eps = int(p.get("decay_rank") or 16), float(p["eps"])
+        if self.n > 256:
+            raise ValueError(f"a state of {self.n} per column is above the scan kernel's limit of 256")
+        self.width = self.heads * self.n
+        self.n_padded = _round_up(self.n, 4)
+        self.shift_off = self.heads * self.n * self.n_padded  # a multiple of 4: the matrices come first, then the last token's input
+        self.record = _round_up(self.shift_off + self.hidden, 4)
+
+    def weights(self) -> dict[str, WeightSpec]:
+        wanted = {"mu." + s: WeightSpec((self.hidden,)) for s in self.MIXES}
+        wanted.update({s: WeightSpec((self.width, self.hidden)) for s in ("r", "k", "v", "g")})
+        wanted.update({"w1": WeightSpec((self.decay_rank, self.hidden), any_extent=(0,)), "w2": WeightSpec((self.width, self.decay_rank), any_extent=(1,)),
+                       "w0": WeightSpec((self.width,)), "u": WeightSpec((self.heads, self.n)), "norm": WeightSpec((self.width,), init="one_plus_normal"),
+                       "o": WeightSpec((self.hidden, self.width))})
+        return wanted
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        f = lambda name: tensors[name].to(torch.float32).contiguous()  # noqa: E731
+        if tensors["w1"].shape[0] != tensors["w2"].shape[1]:
+            raise ValueError(f"the decay's two matrices meet in {tensors['w1'].shape[0]} and {tensors['w2'].shape[1]} entries")
+        self.mu = torch.stack([f("mu." + s) for s in self.MIXES]).contiguous()
+        self.w_in = [tensors[s].contiguous() for s in ("r", "k", "v", "g")]
+        self.w_1, self.w_2, self.w_o = tensors["w1"].contiguous(), tensors["w2"].contiguous(), tensors["o"].contiguous()
+        self.w0, self.bonus, self.norm = f("w0"), f("u").reshape(-1), f("norm")
+
+    def cache_request(self):
+        return RequestState((self.record,), torch.float32)
+
+    def kernel_modules(self):
+        return [("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+
+    def forward(self, x, step, cache, own_cache):
+        if cache is None or not own_cache:
+            raise ValueError("time mixing keeps a state per request; the schedule gave it none")
+        state, slots, rows = cache.state, cache.slots, step.n_rows
+        mixed = recurrent.token_shift_mix(x, self.mu, state, self.shift_off, slots, step.token_row, step.row_start)
+        recurrent.token_shift_keep(x, state, self.shift_off, slots, step.row_start, rows)
+        r, k, v, gate = (ops.linear(mixed[i], w, None, torch.float32) for i, w in enumerate(self.w_in))
+        inner = recurrent.tanh_rows(ops.linear(mixed[4], self.w_1, None, torch.float32), self.dtype)
+        decay_in = ops.linear(inner, self.w_2, None, torch.float32)
+        o = recurrent.wkv_scan(k, r, v, decay_in, 0, self.w0, self.bonus, state, 0, slots, step.row_start, rows, self.heads, self.n, self.n_padded, self.n)
+        y = recurrent.gated_group_norm(o, gate, 0, self.norm, self.n, False, self.eps, self.dtype)
+        return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
 register_mixer("delta_rule", GatedDeltaRule)
 register_mixer("mamba1", SelectiveScanMixer)
 register_mixer("mamba2", StateSpaceMixer)
+register_mixer("wkv", WkvMixer)
