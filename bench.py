@@ -656,6 +656,175 @@ def mirovik_workload(args) -> int:
     return 0
 
 
+KUDAZEN_SIZES = {
+    # width; chunked attention (heads, kv heads, head size, chunk); attention over latents (heads, plain size, rotated size, value size, latent,
+    # query latent); time mixing (heads, head size); feed-forward.  Eight layers A L L W A L L W with tensors of their own, 32,000 tokens
+    "2k": {"width": 2048, "attention": (16, 4, 128, 1024), "latent": (16, 128, 64, 128, 512, 1536), "wkv": (32, 64), "ff": 8192},
+    "4k": {"width": 4096, "attention": (32, 8, 128, 2048), "latent": (32, 128, 64, 128, 512, 1536), "wkv": (64, 64), "ff": 14336},
+}
+
+
+def kudazen_document(size: dict, vocab: int = 32000) -> dict:
+    heads, kv_heads, dim, chunk = size["attention"]
+    mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": chunk}}, "mlp": mlp}
+    l = size["latent"]
+    latent = {"type": "latent_attention", "mixer": {"heads": l[0], "dim": l[1], "rot_dim": l[2], "vdim": l[3], "kv_rank": l[4], "q_rank": l[5],
+                                                    "scale": (l[1] + l[2]) ** -0.5, "rot": {"dims": l[2], "base": 1e6}}, "mlp": mlp}
+    w = size["wkv"]
+    wkv = {"type": "wkv", "mixer": {"heads": w[0], "dim": w[1], "decay_rank": 64}, "mlp": mlp}
+    return {"architecture": "Kudazen", "vocab": vocab, "width": size["width"], "norm": {"eps": 1e-6, "groups": 4},
+            "layers": [attention, latent, latent, wkv, attention, latent, latent, wkv]}
+
+
+def kudazen_kernels(size: dict, measured: dict) -> dict:
+    """The design's own kernels alone at this size, a prompt of 2,048 tokens in one row and 8 rows of one decoded token behind 2,048: time, the
+    bytes each must move against the measured copy bandwidth, for attention the bfloat16 operations against the measured product rate, for
+    the scan the float32 operations; beside each the like kernel of the closest model (Qwen2; for the scan, the package's retention)."""
+    import types
+
+    import torch
+
+    from hyperion_b200 import ops
+    from hyperion_b200.ops import attention as fast, recurrent
+
+    dev = torch.device("cuda")
+    hbm, peak = measured["hbm_gbs"] * 1e9, measured["bf16_tflops"] * 1e12
+    out: dict = {}
+    width, page = size["width"], 16
+
+    def report(name, ms, bytes_moved, fp32_flops=None, bf16_flops=None):
+        entry = {"us": round(ms * 1e3, 2), "bytes": int(bytes_moved), "of_measured_bandwidth": round(bytes_moved / (ms / 1e3) / hbm, 3)}
+        if fp32_flops is not None:
+            entry["fp32_tflops"] = round(fp32_flops / (ms / 1e3) / 1e12, 2)
+        if bf16_flops is not None:
+            entry["of_measured_bf16_rate"] = round(bf16_flops / (ms / 1e3) / peak, 3)
+        out[name] = entry
+
+    for shape, counts, before in (("prefill_2048", [PROMPT], 0), ("decode_8", [1] * 8, PROMPT)):
+        tokens, rows = sum(counts), len(counts)
+        starts = [0]
+        for c in counts:
+            starts.append(starts[-1] + c)
+        row_start = torch.tensor(starts, dtype=torch.int32, device=dev)
+        token_row = torch.tensor([r for r, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=dev)
+        slots = torch.arange(rows, dtype=torch.int32, device=dev)
+        positions = torch.cat([torch.arange(c, dtype=torch.int32) + before for c in counts]).to(dev)
+        context = before + max(counts)
+        per_row = -(-context // page)
+        table = torch.arange(rows * per_row, dtype=torch.int32, device=dev).view(rows, per_row)
+        # the stream's norm and the feed-forward's activation
+        h = torch.randn(tokens, width, device=dev)
+        a, b = (torch.randn(tokens, width, device=dev).to(torch.bfloat16) for _ in range(2))
+        weight = torch.ones(width, device=dev)
+        report(f"add_group_rmsnorm/{shape}", timed(lambda: ops.add_group_rmsnorm(h, a, b, weight, 4, 1e-6, torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2 + 2))
+        report(f"qwen2.add_rmsnorm/{shape}", timed(lambda: ops.add_rmsnorm(h, a, weight, 1e-6, torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2))
+        gu = torch.randn(tokens, 2 * size["ff"], device=dev).to(torch.bfloat16)
+        report(f"clamped_glu/{shape}", timed(lambda: ops.clamped_glu(gu, 7.0, 1.702)), tokens * size["ff"] * 6)
+        report(f"qwen2.swiglu/{shape}", timed(lambda: ops.swiglu(gu)), tokens * size["ff"] * 6)
+        # chunked attention with slopes in the tensor-core kernels, beside the same kernels as Qwen2 calls them (no chunk, no table)
+        heads, kv_heads, dim, chunk = size["attention"]
+        proj = torch.randn(tokens, (heads + 2 * kv_heads) * dim, device=dev)
+        cache = (torch.randn(rows * per_row, 2, kv_heads, page, dim, device=dev) * 0.5).to(torch.bfloat16)
+        q = torch.empty(tokens, heads * dim, dtype=torch.bfloat16, device=dev)
+        temp = torch.ones(heads, device=dev)
+        report(f"attention.prepare/{shape}", timed(lambda: ops.heads_prepare_wide(proj, 0, heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim, dim, positions, q_out=q,
+                                                                               cache=cache, block_table=table, token_row=token_row, page_size=page, v_unit_eps=1e-6,
+                                                                               q_head_scale=temp)), tokens * (heads + 2 * kv_heads) * dim * 6)
+        slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / heads) for i in range(heads)], device=dev)
+        by_distance = (-(slopes[:, None] * torch.arange(chunk, device=dev)[None, :]) * 1.4426950408889634).contiguous()
+        attn = torch.empty(tokens, heads * dim, dtype=torch.bfloat16, device=dev)
+        fake_rows = [types.SimpleNamespace(count=c, position=before) for c in counts]
+        tile = fast.tile_rows(dim, page)
+        tiles, items = fast.plan(fake_rows, fast.tile_tokens(heads, kv_heads, tile))
+        seen_chunked = sum(min(p % chunk + 1, p + 1) for p in positions.tolist())
+        seen_all = sum(p + 1 for p in positions.tolist())
+        for label, window, bias, seen in (("attention.chunked_sloped", -chunk, by_distance, seen_chunked), ("qwen2.attention", 0, None, seen_all)):
+            if len(tiles):
+                t_dev = torch.tensor(tiles, dtype=torch.int32, device=dev)
+                run = lambda: fast.attention_tiles(q, heads, cache, table, token_row, positions, t_dev, len(tiles) // 3, dim ** -0.5, window, attn, tile_size=tile, bias=bias)
+            else:
+                i_dev = torch.tensor(items, dtype=torch.int32, device=dev)
+                splits = fast.choose_splits(len(items), heads, kv_heads, min(context, chunk + fast.KEY_TILE) if window else context)
+                space = torch.empty(len(items) * heads * max(splits, 1) * (dim + 2), dtype=torch.float32, device=dev)
+                run = lambda: fast.attention_tokens(q, heads, cache, table, token_row, positions, i_dev, len(items), splits, dim ** -0.5, window, attn, workspace=space, bias=bias)
+            keys_read = rows * min(context, chunk if window else context) * 2 * kv_heads * dim * 2
+            report(f"{label}/{shape}", timed(run), keys_read + tokens * heads * dim * 4, bf16_flops=4.0 * seen * heads * dim)
+        # attention over latents: the records, the queries, attention itself (one key/value head of kv_rank + rot_dim entries for all heads)
+        l_heads, l_dim, l_rot, l_vdim, rank, q_rank = size["latent"]
+        record = rank + l_rot
+        down = torch.randn(tokens, q_rank + record, device=dev)
+        l_cache = (torch.randn(rows * per_row, 1, page, record, device=dev) * 0.3).to(torch.bfloat16)
+        ones_q, ones_kv = torch.ones(q_rank, device=dev), torch.ones(rank, device=dev)
+        inv_freq = torch.rand(l_rot // 2, device=dev)
+        report(f"latent.prepare/{shape}", timed(lambda: ops.latent_prepare(down, 0, q_rank, q_rank, rank, l_rot, ones_q, ones_kv, 1e-6, inv_freq, l_rot, positions, torch.bfloat16,
+                                                                          l_cache, table, token_row, page)), tokens * (q_rank + record) * 6)
+        uq = torch.randn(tokens, l_heads * (l_dim + l_rot), device=dev).to(torch.bfloat16)
+        q_lat = torch.randn(l_heads, tokens, rank, device=dev)
+        report(f"latent.query/{shape}", timed(lambda: ops.latent_query(uq, q_lat, l_heads, l_dim, l_rot, inv_freq, l_rot, positions)),
+               tokens * l_heads * (rank * 4 + l_rot * 2 + record * 2))
+        query = ops.latent_query(uq, q_lat, l_heads, l_dim, l_rot, inv_freq, l_rot, positions)
+        sinks = torch.zeros(l_heads, device=dev)
+        report(f"latent.attention/{shape}", timed(lambda: ops.attention_general(query, l_heads, 1, record, rank, l_cache, table, token_row, positions, page, record ** -0.5,
+                                                                              sinks=sinks, value_prefix=True), reps=5),
+               rows * context * record * 2 + tokens * l_heads * (record + rank) * 2, bf16_flops=2.0 * seen_all * l_heads * (record + rank))
+        # time mixing: the five mixes, the scan, the gated unit norm; beside the scan, the package's retention at the same sizes
+        w_heads, n = size["wkv"]
+        x = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+        mu = torch.rand(5, width, device=dev)
+        state = torch.zeros(rows, w_heads * n * n + width, device=dev)
+        report(f"wkv.shift_mix/{shape}", timed(lambda: recurrent.token_shift_mix(x, mu, state, w_heads * n * n, slots, token_row, row_start)), tokens * width * 12)
+        k, r, v, d = (torch.randn(tokens, w_heads * n, device=dev) * 0.5 for _ in range(4))
+        w0, bonus = torch.full((w_heads * n,), -3.0, device=dev), torch.rand(w_heads * n, device=dev)
+        scan = lambda: recurrent.wkv_scan(k, r, v, d, 0, w0, bonus, state, 0, slots, row_start, rows, w_heads, n, n, n)
+        moved = 4 * (tokens * 5 * w_heads * n + 2 * rows * w_heads * n * n)
+        report(f"wkv.scan/{shape}", timed(scan), moved, fp32_flops=5.0 * tokens * w_heads * n * n)
+        o = scan()
+        report(f"wkv.gated_norm/{shape}", timed(lambda: recurrent.gated_group_norm(o, d, 0, w0, n, False, 1e-6, torch.bfloat16)), tokens * w_heads * n * (4 + 4 + 2))
+        kqv = torch.cat([k, r, v], dim=1).contiguous()
+        decay = torch.full((w_heads,), 0.99, device=dev)
+        like = lambda: recurrent.state_scan(recurrent.MODE_RETENTION, kqv, 0, w_heads * n, 2 * w_heads * n, kqv, 0, 0, decay, decay, None, state, 0, slots, row_start,
+                                            rows, w_heads, w_heads, n, n, n)
+        report(f"mirovik.retention_scan/{shape}", timed(like), 4 * (tokens * 4 * w_heads * n + 2 * rows * w_heads * n * n), fp32_flops=4.0 * tokens * w_heads * n * n)
+    return out
+
+
+def kudazen_workload(args) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 from a context of 2,048) of the Kudazen design at two sizes that
+    resemble real layers, beside the closest model of the package, Qwen2, at equal width, heads, feed-forward and number of layers;
+    random weights."""
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import KudazenConfig, Qwen2Config
+
+    measured, kind = peaks()
+    for name, size in KUDAZEN_SIZES.items():
+        if args.size and name != args.size:
+            continue
+        heads, kv_heads, dim, _ = size["attention"]
+        arms = {
+            "kudazen": ("Kudazen", KudazenConfig.from_dict(kudazen_document(size))),
+            "qwen2": ("Qwen2ForCausalLM", Qwen2Config(num_hidden_layers=8, hidden_size=size["width"], intermediate_size=size["ff"], num_attention_heads=heads,
+                                                      num_key_value_heads=kv_heads, head_dim=dim, vocab_size=32000, max_position_embeddings=8192,
+                                                      rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)),
+        }
+        line = {"workload": "kudazen", "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids", "layers": "A L L W A L L W",
+                "peaks": kind}
+        for arm, (architecture, config) in arms.items():
+            engine = Engine.from_random(architecture, config, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (PROMPT + 256), max_requests=8)
+            prefill = time_prefill(engine)
+            decode = time_decode(engine, 8, 16, max(3, args.warmup), decode_tokens=max(3, args.warmup) + 160)
+            line[arm] = {"prefill_ms": round(prefill["ms"], 3), "prefill_tokens_per_s": round(PROMPT / prefill["ms"] * 1e3),
+                         "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tok_s"], 1),
+                         "decode_launches_per_step": round(decode["launches"] / decode["steps"], 1)}
+            del engine
+            torch.cuda.empty_cache()
+        line["kernels"] = kudazen_kernels(size, measured)
+        print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -668,13 +837,13 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
-    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik", "mirovik"],
+    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik", "mirovik", "kudazen"],
                         help="one of the other workloads instead: 128 requests with prompts of 16..4096 tokens and 256 decoded tokens "
                              "each through generate() at the 1.5B shape; batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape; "
                              "or the reference's own published tables (decode by batch at context 512, prefill by length) at the 0.5B and 7B shapes; "
                              "or the Nunivik design at two layer sizes beside the Qwen2 model of equal size, with its own kernels timed alone; "
                              "or the Mirovik design at two layer sizes beside the Nunivik model of equal size, likewise")
-    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik or mirovik: one of its sizes only")
+    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik, mirovik or kudazen: one of its sizes only")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -684,6 +853,8 @@ def main() -> int:
         return nunivik_workload(args)
     if args.workload == "mirovik":
         return mirovik_workload(args)
+    if args.workload == "kudazen":
+        return kudazen_workload(args)
     if args.workload:
         return other_workload(args.workload)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

@@ -228,14 +228,14 @@ __global__ void __launch_bounds__(THREADS) attention_tiles_kernel(AttnArgs a, co
         const int tok = v / gc, hh = v - tok * gc;
         const bool valid = tok < ntok && hh < heads_here;
         hi[r] = valid ? pos_first + tok : -1;
-        lo[r] = (valid && a.window > 0) ? max(0, hi[r] - a.window + 1) : 0;
+        lo[r] = valid ? first_seen(hi[r], a.window) : 0;
     }
     const int warp_hi = pos_first + min(ntok - 1, (warp * 16 + 15) / gc);
     const int warp_first_tok = (warp * 16) / gc;
-    const int warp_lo = a.window > 0 ? max(0, pos_first + warp_first_tok - a.window + 1) : 0;
+    const int warp_lo = first_seen(pos_first + warp_first_tok, a.window);
     const bool warp_has_rows = warp_first_tok < ntok;
 
-    const int need_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    const int need_lo = first_seen(pos_first, a.window);
     const int start = (need_lo / BN) * BN;
     const int n_tiles = (pos_last - start) / BN + 1;
     RowState st;
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(THREADS) attention_tokens_kernel(AttnArgs a, c
     const int heads_here = min(16, group - chunk * 16);
     const int pos = a.positions[t];
     const int* table = a.block_table + (size_t)a.token_row[t] * a.table_width;
-    const int need_lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int need_lo = first_seen(pos, a.window);
     const int start = (need_lo / BN) * BN;
     const int n_tiles = (pos - start) / BN + 1;
     const int per_split = (n_tiles + splits - 1) / splits;

@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
         it.heads_here = min(gc, group - chunk * gc);
         it.pos_first = info[4];
         it.pos_last = it.pos_first + it.ntok - 1;
-        it.need_lo = a.window > 0 ? max(0, it.pos_first - a.window + 1) : 0;
+        it.need_lo = first_seen(it.pos_first, a.window);
         it.start = (it.need_lo / BN) * BN;
         it.n_tiles = (it.pos_last - it.start) / BN + 1;
         it.halves = it.ntok * gc > BM ? 2 : 1;
@@ -498,7 +498,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
                 // A row beyond the tile's end (or beyond the heads of the chunk) is computed like the tile's last token and never
                 // stored: it takes the same way through the code as its neighbours, so no warp has to walk two ways.
                 const int hi = row_valid ? it.pos_first + tok : it.pos_last;
-                const int lo = a.window > 0 ? max(0, hi - a.window + 1) : 0;
+                const int lo = first_seen(hi, a.window);
                 float m = -INFINITY, l = 0.f;
                 for (int j = 0; j < n_tiles; ++j) {
                     const int h = hx + j;

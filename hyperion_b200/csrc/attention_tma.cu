@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
     const int heads_here = min(gc, group - chunk * gc);
     const int* table = a.block_table + (size_t)brow * a.table_width;
     const int pos_first = a.positions[tok0], pos_last = pos_first + ntok - 1;
-    const int need_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    const int need_lo = first_seen(pos_first, a.window);
     const int start = (need_lo / BN) * BN;
     const int n_tiles = (pos_last - start) / BN + 1;
     int first = 0, last = n_tiles;
@@ -355,12 +355,12 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         const int tok = v / gc, hh = v - tok * gc;
         const bool valid = tok < ntok && hh < heads_here;
         hi[r] = valid ? pos_first + tok : -1;
-        lo[r] = (valid && a.window > 0) ? max(0, hi[r] - a.window + 1) : 0;
+        lo[r] = valid ? first_seen(hi[r], a.window) : 0;
         bias[r] = (valid && a.bias) ? a.bias + (size_t)(first_head + hh) * a.bias_span : nullptr;
     }
     const int warp_first_tok = TOKENS ? 0 : (warp * 16) / gc;
     const int warp_hi = pos_first + (TOKENS ? 0 : min(ntok - 1, (warp * 16 + 15) / gc));
-    const int warp_lo = a.window > 0 ? max(0, pos_first + warp_first_tok - a.window + 1) : 0;
+    const int warp_lo = first_seen(pos_first + warp_first_tok, a.window);
     const bool warp_has_rows = warp_first_tok < ntok;
     RowState st;
     st.init();

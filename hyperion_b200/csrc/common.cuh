@@ -125,3 +125,12 @@ static inline int launch_after_previous(void (*kernel)(Params...), dim3 grid, di
     config.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
+
+// The first position that a query at position `pos` sees.  window > 0: the last `window` positions (pos - window + 1 at the least);
+// window < 0: the query's own chunk of -window positions, chunks counted from position 0; window == 0: everything.
+// It never falls as pos grows, so a tile's first query gives the tile's lowest bound.
+__host__ __device__ __forceinline__ int first_seen(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos >= 0 ? pos - pos % (-window) : 0;
+    return 0;
+}

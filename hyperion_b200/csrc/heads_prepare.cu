@@ -112,7 +112,7 @@ HB_EXPORT int hb_heads_prepare(void* x, int is_bf16, int tokens, int stride, int
 //   * the RMS norm of queries (and of keys) may run over the whole projection, all heads at once, with a weight per
 //     column of the projection (norm_whole), instead of per head with one weight for all heads,
 //   * the rotation may pair dimension i with i + rot_dims / 2 (rot_half) instead of 2i with 2i + 1,
-//   * keys are multiplied by k_scale after the rotation.
+//   * keys are multiplied by k_scale after the rotation, queries by a factor per head (q_head_scale, or none).
 // Every thread reads and writes whole pairs, so the float-to-float case may work in place.
 namespace {
 template <typename TO>
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
     int rot_dims, int rot_half, const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride,
     TO* __restrict__ k_cache, TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps,
-    int* status) {
+    const float* __restrict__ q_head_scale, int* status) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, head = blockIdx.y;  // q heads, then k heads, then v heads
     const int pos = positions[t];
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
         else if (k_cache) dst = page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)local * head_stride + (size_t)slot * token_stride : nullptr;
         else dst = k_out + (size_t)t * k_out_stride + (size_t)local * head_dim;
         if (!dst) return;
-        const float post = is_q ? 1.f : k_scale;
+        const float post = is_q ? (q_head_scale ? q_head_scale[local] : 1.f) : k_scale;
         const int pairs = inv_freq ? rot_dims / 2 : 0;
         for (int i = threadIdx.x; i < pairs; i += THREADS) {
             const int a = rot_half ? i : 2 * i, b = rot_half ? i + pairs : 2 * i + 1;
@@ -192,8 +192,8 @@ constexpr int TOKEN_THREADS = 256, MAX_PAIRS = 128;
 
 // Heads first .. first + heads - 1 of a projection whose head 0 starts at `all`.
 template <typename TO, typename Place>
-__device__ __forceinline__ void prepare_heads_of_token(const float* all, int first, int heads, int head_dim, const float* w, float inv, float post, int pairs,
-                                                       int rot_half, const float* cs, const float* sn, Place place) {
+__device__ __forceinline__ void prepare_heads_of_token(const float* all, int first, int heads, int head_dim, const float* w, float inv, float post,
+                                                       const float* head_post, int pairs, int rot_half, const float* cs, const float* sn, Place place) {
     for (int item = threadIdx.x; item < heads * pairs; item += TOKEN_THREADS) {
         const int head = first + item / pairs, i = item % pairs;
         const int a = rot_half ? i : 2 * i, b = rot_half ? i + pairs : 2 * i + 1;
@@ -202,15 +202,16 @@ __device__ __forceinline__ void prepare_heads_of_token(const float* all, int fir
         const float u = p[a] * inv * (wh ? wh[a] : 1.f), v = p[b] * inv * (wh ? wh[b] : 1.f);
         TO* dst = place(head);
         if (!dst) continue;
-        dst[a] = from_float<TO>((u * cs[i] - v * sn[i]) * post);
-        dst[b] = from_float<TO>((v * cs[i] + u * sn[i]) * post);
+        const float after = head_post ? post * head_post[head] : post;
+        dst[a] = from_float<TO>((u * cs[i] - v * sn[i]) * after);
+        dst[b] = from_float<TO>((v * cs[i] + u * sn[i]) * after);
     }
     const int rest = head_dim - 2 * pairs;
     for (int item = threadIdx.x; item < heads * rest; item += TOKEN_THREADS) {
         const int head = first + item / rest, d = 2 * pairs + item % rest;
         TO* dst = place(head);
         if (!dst) continue;
-        dst[d] = from_float<TO>(all[(size_t)head * head_dim + d] * inv * (w ? w[(size_t)head * head_dim + d] : 1.f) * post);
+        dst[d] = from_float<TO>(all[(size_t)head * head_dim + d] * inv * (w ? w[(size_t)head * head_dim + d] : 1.f) * (head_post ? post * head_post[head] : post));
     }
 }
 
@@ -220,7 +221,7 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims, int rot_half,
     const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride, TO* __restrict__ k_cache,
     TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride, const int* __restrict__ block_table, int table_width,
-    const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps, int* status) {
+    const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps, const float* __restrict__ q_head_scale, int* status) {
     __shared__ float scratch[32];
     __shared__ float cs[MAX_PAIRS], sn[MAX_PAIRS];
     const int t = blockIdx.x;
@@ -255,11 +256,11 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
     const int q_each = (q_heads + parts - 1) / parts, k_each = (kv_heads + parts - 1) / parts;
     const int q_first = min(q_heads, part * q_each), q_count = min(q_heads, q_first + q_each) - q_first;
     const int k_first = min(kv_heads, part * k_each), k_count = min(kv_heads, k_first + k_each) - k_first;
-    prepare_heads_of_token<TO>(row + q_off, q_first, q_count, head_dim, q_norm, inv_q, 1.f, pairs, rot_half, cs, sn,
+    prepare_heads_of_token<TO>(row + q_off, q_first, q_count, head_dim, q_norm, inv_q, 1.f, q_head_scale, pairs, rot_half, cs, sn,
                                [&](int head) { return q_out + (size_t)t * q_out_stride + (size_t)head * head_dim; });
     if (k_cache) {
         TO* key_page = page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)slot * token_stride : nullptr;
-        prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
+        prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, nullptr, pairs, rot_half, cs, sn,
                                    [&](int head) { return key_page ? key_page + (size_t)head * head_stride : nullptr; });
         if (page >= 0 && v_unit_eps >= 0.f) {  // every value head leaves with a root mean square of one: a warp per head
             TO* value_page = v_cache + (size_t)page * page_stride + (size_t)slot * token_stride;
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
             }
         }
     } else {
-        prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
+        prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, nullptr, pairs, rot_half, cs, sn,
                                    [&](int head) { return k_out + (size_t)t * k_out_stride + (size_t)head * head_dim; });
     }
 }
@@ -292,7 +293,7 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                     int rot_half, const int* positions, float k_scale, void* q_out, int q_out_stride, void* k_out, int k_out_stride,
                                     int out_is_bf16, void* k_cache, void* v_cache, long long page_stride, long long head_stride, int token_stride,
                                     const int* block_table, int table_width, const int* token_row, int page_size, int pages, float v_unit_eps,
-                                    int* status, cudaStream_t stream) {
+                                    const float* q_head_scale, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1) || !q_out || (!k_cache && !k_out)) return HB_UNSUPPORTED_SIZE;
     const int heads = q_heads + kv_heads + (k_cache ? kv_heads : 0);
@@ -307,13 +308,13 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                              (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                              (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width,
-                                                                             token_row, page_size, pages, v_unit_eps, status);
+                                                                             token_row, page_size, pages, v_unit_eps, q_head_scale, status);
         else
             heads_prepare_token_kernel<<<token_grid, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                              (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                              (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size,
-                                                                             pages, v_unit_eps, status);
+                                                                             pages, v_unit_eps, q_head_scale, status);
         return launch_status();
     }
     const dim3 grid(tokens, heads);
@@ -322,13 +323,13 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                                                 eps, inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                 (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                 (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width, token_row,
-                                                                page_size, pages, v_unit_eps, status);
+                                                                page_size, pages, v_unit_eps, q_head_scale, status);
     else
         heads_prepare_wide_kernel<<<grid, THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, norm_whole,
                                                                 eps, inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                 (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                 (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size, pages,
-                                                                v_unit_eps, status);
+                                                                v_unit_eps, q_head_scale, status);
     return launch_status();
 }
 

@@ -285,14 +285,16 @@ def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_he
                        k_norm: torch.Tensor | None = None, norm_whole: bool = False, eps: float = 0.0, inv_freq: torch.Tensor | None = None,
                        rot_dims: int = 0, rot_half: bool = False, k_scale: float = 1.0, cache: torch.Tensor | None = None,
                        block_table: torch.Tensor | None = None, token_row: torch.Tensor | None = None, page_size: int = 0,
-                       v_unit_eps: float | None = None) -> None:
+                       v_unit_eps: float | None = None, q_head_scale: torch.Tensor | None = None) -> None:
     """Float projections ``x`` [tokens, *] with queries at column ``q_off``, keys at ``k_off``, values at ``v_off``: query/key
     norm (per head with one weight, or over the whole projection with a weight per column), rotation (adjacent pairs, or
     dimension i with i + rot_dims / 2), keys times ``k_scale``; queries to ``q_out`` [tokens, >= q_heads * head_dim], keys and
     values into ``cache`` (either arrangement of :func:`paged_strides`) or keys to ``k_out`` (values then stay where they are).
     ``q_out`` and ``k_out`` may be float views of ``x`` itself.  ``v_unit_eps`` (with a cache): every value head is divided by
-    sqrt(mean(v^2) + v_unit_eps) before it is stored."""
-    require_cuda(x, positions, q_out, k_out, q_norm, k_norm, inv_freq, cache, block_table, token_row)
+    sqrt(mean(v^2) + v_unit_eps) before it is stored.  ``q_head_scale`` [q_heads] float: a factor on every query head, after norm and rotation."""
+    require_cuda(x, positions, q_out, k_out, q_norm, k_norm, inv_freq, cache, block_table, token_row, q_head_scale)
+    if q_head_scale is not None and (q_head_scale.dtype != torch.float32 or q_head_scale.numel() != q_heads or not q_head_scale.is_contiguous()):
+        raise KernelError("heads_prepare_wide: the queries' factors are a dense float32 vector with one entry per head")
     if x.dtype != torch.float32 or x.stride(-1) != 1 or q_out.stride(-1) != 1 or (k_out is not None and (k_out.stride(-1) != 1 or k_out.dtype != q_out.dtype)):
         raise KernelError("heads_prepare_wide: float32 projections and outputs with unit inner stride")
     for t in (q_norm, k_norm, inv_freq):
@@ -313,7 +315,7 @@ def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_he
         i32(1 if rot_half else 0), ptr(positions), f32(k_scale), ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
         i32(k_out.stride(0) if k_out is not None else 0), i32(is_bf16(q_out)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
         ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1] if block_table is not None else 0),
-        ptr(token_row), i32(page_size), i32(pages), f32(-1.0 if v_unit_eps is None else v_unit_eps), ptr(status_word(x.device)), stream_ptr()),
+        ptr(token_row), i32(page_size), i32(pages), f32(-1.0 if v_unit_eps is None else v_unit_eps), ptr(q_head_scale), ptr(status_word(x.device)), stream_ptr()),
         "heads_prepare_wide")
 
 

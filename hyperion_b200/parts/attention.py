@@ -151,8 +151,8 @@ class GroupedQueryAttention(Mixer):
         if n_items:
             # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
             longest = step.host.get("context_cap") or self._longest_short_row(step.rows)
-            if self.window:
-                longest = min(longest, self.window + fast_attention.KEY_TILE)
+            if self.window:  # a window, or (negative) a chunk: no token reads more keys than that
+                longest = min(longest, abs(self.window) + fast_attention.KEY_TILE)
             splits = fast_attention.choose_splits(n_items, self.heads, self.kv_heads, longest)
             fast_attention.attention_tokens(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
                                             step.extra["attn_items"], n_items, splits, self.scale, self.window, out, softcap=self.softcap, bias=bias)

@@ -9,8 +9,12 @@ rotated.  Values may be divided by their root mean square per head before they a
 Keys of ``head_dim`` and values of ``value_dim`` lie in pages like every other attention's of the package.
 
 Per step: one product to [q | k | v] kept in float; one kernel (``csrc/heads_prepare.cu``) that norms the values and writes keys
-and values to their pages and the queries to a dense buffer; attention of every token over its request's pages
-(``csrc/attention_generic.cu``: scores, factor, slope and softmax in float); the output projection.
+and values to their pages and the queries to a dense buffer; attention of every token over its request's pages; the output
+projection.  In bfloat16, with keys and values of one size that is a multiple of 64 and chunks of at most ``LONGEST_TABLE``
+positions, attention runs in the tensor-core kernels of the package's other attentions (tcgen05 tiles for prompt portions, split
+keys for decoded tokens): inside a chunk no distance exceeds the chunk, so the slopes become a table by distance, the chunk is
+those kernels' window argument with a negative sign, and the head's factor multiplies its query (in float, before the query's one
+rounding).  Everything else, and float32, runs in ``csrc/attention_generic.cu`` (scores, factor, slope and softmax in float).
 
 Parameters: ``hidden_size``, ``heads``, ``kv_heads``, ``head_dim``, ``value_dim`` (``head_dim`` unless stated), ``scale``, ``chunk``,
 ``slopes`` (one per head, or None), ``head_temperature`` (bool: the tensor ``temp`` [heads]), ``value_unit_rms`` (bool), ``eps``.
@@ -20,13 +24,18 @@ from __future__ import annotations
 
 from typing import Mapping
 
+import math
+
 import torch
 
 from .. import ops
+from ..ops import attention as fast_attention
+from .attention import GroupedQueryAttention
 from .base import BuildContext, Mixer, PagedKV, PagedTokens, WeightSpec, register_mixer
 from .spec import PartSpec
 
 LARGEST_HEAD = 640  # csrc/attention_generic.cu
+LONGEST_TABLE = 16384  # chunks up to this many positions get their slopes as a table by distance
 
 
 def _common_dtype(tensors) -> torch.dtype:
@@ -56,6 +65,13 @@ class SlopedAttention(Mixer):
         self.q_width, self.k_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
         self.v_width, self.core_width = self.kv_heads * self.value_dim, self.heads * self.value_dim
         self.temp = None
+        self.window, self.softcap = -self.chunk, 0.0  # as the tensor-core kernels take them: a negative window is a chunk
+        self.fast = (self.dtype == torch.bfloat16 and self.value_dim == self.head_dim and self.head_dim % 64 == 0 and fast_attention.supported(self.head_dim)
+                     and (self.slopes is None or 0 < self.chunk <= LONGEST_TABLE))
+        self.by_distance_log2 = None
+        if self.fast and self.slopes is not None:  # [heads, chunk]: minus slope times distance, in the base-2 units of those kernels' softmax
+            distance = torch.arange(self.chunk, dtype=torch.float32, device=build.device)
+            self.by_distance_log2 = (-(self.slopes[:, None] * distance[None, :]) * math.log2(math.e)).contiguous()
 
     def weights(self) -> dict[str, WeightSpec]:
         wanted = {"q": WeightSpec((self.q_width, self.hidden)), "k": WeightSpec((self.k_width, self.hidden)), "v": WeightSpec((self.v_width, self.hidden)),
@@ -77,16 +93,31 @@ class SlopedAttention(Mixer):
         return PagedTokens((self.kv_heads,), (self.head_dim + self.value_dim,), 0)
 
     def kernel_modules(self):
-        return [("heads_prepare", {}), ("attention_generic", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        modules = [("heads_prepare", {}), ("attention_generic", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        if self.fast:  # which is launched depends on the page size of the cache
+            modules += [("elementwise", {}), ("attention_tma", {"HB_HEAD_DIM": self.head_dim})]
+            if self.head_dim in (64, 128):
+                modules.append(("attention_tcgen05", {"HB_HEAD_DIM": self.head_dim}))
+        return modules
+
+    def step_plans(self):
+        return GroupedQueryAttention.step_plans(self)
+
+    _attend_fast = GroupedQueryAttention._attend_fast
+    _longest_short_row = staticmethod(GroupedQueryAttention._longest_short_row)
 
     def forward(self, x, step, cache, own_cache):
         if cache is None or not own_cache:
             raise ValueError("this attention writes a paged cache of its own; the schedule gave it none")
         proj = ops.linear(x, self.w_qkv, None, torch.float32)
         q = torch.empty((x.shape[0], self.q_width), dtype=self.dtype, device=x.device)
+        fast = self.fast and fast_attention.takes_distance_bias(self.head_dim, cache.page_size)
         ops.heads_prepare_wide(proj, 0, self.q_width, self.q_width + self.k_width, self.heads, self.kv_heads, self.head_dim, self.value_dim, step.positions,
                                q_out=q, cache=cache.kv, block_table=cache.block_table, token_row=step.token_row, page_size=cache.page_size,
-                               v_unit_eps=self.eps if self.value_unit_rms else None)
+                               v_unit_eps=self.eps if self.value_unit_rms else None, q_head_scale=self.temp if fast else None)
+        if fast:
+            attn = self._attend_fast(q, step, cache, bias=self.by_distance_log2)
+            return ops.linear(attn, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
         attn = ops.attention_general(q, self.heads, self.kv_heads, self.head_dim, self.value_dim, cache.kv, cache.block_table, step.token_row, step.positions,
                                      cache.page_size, self.scale, head_scale=self.temp, slopes=self.slopes, chunk=self.chunk)
         return ops.linear(attn, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
