@@ -765,9 +765,13 @@ def kudazen_kernels(size: dict, measured: dict) -> dict:
                tokens * l_heads * (rank * 4 + l_rot * 2 + record * 2))
         query = ops.latent_query(uq, q_lat, l_heads, l_dim, l_rot, inv_freq, l_rot, positions)
         sinks = torch.zeros(l_heads, device=dev)
-        report(f"latent.attention/{shape}", timed(lambda: ops.attention_general(query, l_heads, 1, record, rank, l_cache, table, token_row, positions, page, record ** -0.5,
-                                                                              sinks=sinks, value_prefix=True), reps=5),
-               rows * context * record * 2 + tokens * l_heads * (record + rank) * 2, bf16_flops=2.0 * seen_all * l_heads * (record + rank))
+        latent_flops = 2.0 * seen_all * l_heads * (record + rank)
+        latent_bytes = rows * context * record * 2 + tokens * l_heads * (record + rank) * 2
+        report(f"latent.attention/{shape}", timed(lambda: fast.attention_latent(query, l_heads, record, rank, l_cache, table, row_start, positions, rows, max(counts),
+                                                                              context, record ** -0.5, sinks=sinks), reps=5), latent_bytes, bf16_flops=latent_flops)
+        report(f"latent.attention_float_lanes/{shape}", timed(lambda: ops.attention_general(query, l_heads, 1, record, rank, l_cache, table, token_row, positions, page,
+                                                                                          record ** -0.5, sinks=sinks, value_prefix=True), reps=3),
+               latent_bytes, bf16_flops=latent_flops)
         # time mixing: the five mixes, the scan, the gated unit norm; beside the scan, the package's retention at the same sizes
         w_heads, n = size["wkv"]
         x = torch.randn(tokens, width, device=dev).to(torch.bfloat16)

@@ -169,3 +169,63 @@ def attention_tokens(q, heads, cache, block_table, token_row, positions, items, 
         from . import native
 
         native.LAUNCHES[0] += 1  # the merge kernel
+
+
+# ------------------------------------------------------------------ attention over latent records (csrc/attention_latent.cu)
+LATENT_LARGEST_RECORD = 640
+
+
+def latent_supported(record: int, value: int) -> bool:
+    """Records whose size is a multiple of 16 (up to 640) with values, their first entries, a multiple of 8."""
+    return record % 16 == 0 and value % 8 == 0 and 0 < value <= record <= LATENT_LARGEST_RECORD
+
+
+def choose_latent_shape(rows: int, longest_count: int, heads: int, longest_context: int, sms: int | None = None) -> tuple[bool, int]:
+    """(blocks of 32 rows instead of 16, splits of the keys): 32 rows as soon as one request brings more than 16 (token, head) pairs;
+    the keys are split only when the blocks would leave most of the device idle, into shares of at least two key tiles."""
+    wide = longest_count * heads > 16
+    blocks = rows * -(-longest_count * heads // (32 if wide else 16))
+    key_tiles = -(-longest_context // KEY_TILE)
+    sms = sms or sm_count()
+    if 2 * blocks > sms:
+        return wide, 1
+    return wide, max(1, min(sms // blocks, key_tiles // 2, 64))
+
+
+def attention_latent(query: torch.Tensor, heads: int, record: int, value: int, cache: torch.Tensor, block_table: torch.Tensor, row_start: torch.Tensor,
+                     positions: torch.Tensor, n_rows: int, longest_count: int, longest_context: int, scale: float, sinks: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, shape: tuple[bool, int] | None = None) -> torch.Tensor:
+    """Causal attention of ``heads`` query heads over one shared key/value head: ``query`` [tokens, heads * record] bfloat16 meets the
+    records of ``cache`` [pages, 1, page_size, record]; a record's first ``value`` entries are its value.  ``row_start`` [rows + 1] int32:
+    the tokens of each request row (consecutive positions); ``longest_count`` the most tokens of a row and ``longest_context`` the
+    largest position plus one (they size the launch).  ``sinks`` [heads] float: one more term exp(sink) in each softmax's denominator.
+    Returns [tokens, heads * value]."""
+    require_cuda(query, cache, block_table, row_start, positions, sinks, out, workspace)
+    tokens = query.shape[0]
+    if query.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or query.stride(-1) != 1 or query.shape[1] != heads * record:
+        raise KernelError("attention_latent: bfloat16 queries of [tokens, heads * record]")
+    if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != record or not cache.is_contiguous() or not latent_supported(record, value):
+        raise KernelError("attention_latent: a dense cache of [pages, 1, page_size, record], records a multiple of 16 up to 640, values a multiple of 8")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != heads or not sinks.is_contiguous()):
+        raise KernelError("attention_latent: sinks are a dense float32 vector with one entry per head")
+    if out is None:
+        out = torch.empty((tokens, heads * value), dtype=torch.bfloat16, device=query.device)
+    elif out.dtype != torch.bfloat16 or out.shape[0] != tokens or out.shape[1] < heads * value or out.stride(1) != 1:
+        raise KernelError("attention_latent: the output is a bfloat16 [tokens, >= heads * value] view")
+    wide, splits = shape if shape is not None else choose_latent_shape(n_rows, longest_count, heads, longest_context)
+    if splits > 1:
+        need = tokens * heads * splits * (value + 2)
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.float32, device=query.device)
+        elif workspace.numel() < need or workspace.dtype != torch.float32:
+            raise KernelError(f"attention_latent: workspace of {need} floats needed")
+    pages, _, page_size, _ = cache.shape
+    check(library("attention_latent", HB_RECORD=record, HB_VALUE=value).hb_attention_latent(
+        ptr(query), i32(query.stride(0)), ptr(out), i32(out.stride(0)), ptr(workspace if splits > 1 else None), ptr(cache), ptr(block_table),
+        i32(block_table.shape[1]), ptr(row_start), ptr(positions), ptr(sinks), i32(tokens), i32(n_rows), i32(longest_count), i32(heads), i32(page_size),
+        i32(pages), i32(splits), i32(1 if wide else 0), f32(scale), ptr(status_word(query.device)), stream_ptr()), "attention_latent")
+    if splits > 1:
+        from . import native
+
+        native.LAUNCHES[0] += 1  # the merge kernel
+    return out

@@ -14,8 +14,10 @@ the latent's space by a batched product with V_h.  Norms, angles, scores and sof
 
 Per step: one product for both down-projections (kept in float); one kernel that norms the latents, rotates the shared key part
 and writes the record to its page (``csrc/heads_prepare.cu``); the queries' up-projection; the batched product with K_h; one
-kernel that puts the query of every head together (rotating its rotated part); attention (``csrc/attention_generic.cu``); the
-batched product with V_h; the output projection.
+kernel that puts the query of every head together (rotating its rotated part); attention; the batched product with V_h; the
+output projection.  In bfloat16, with records of a multiple of 16 entries and latents of a multiple of 8, attention runs on the
+tensor cores (``csrc/attention_latent.cu``: blocks of 16 or 32 (token, head) pairs over key tiles of 64 records, the keys split over
+several blocks when a step brings few tokens).  Everything else, and float32, runs in ``csrc/attention_generic.cu``.
 
 Parameters: ``hidden_size``, ``heads``, ``head_dim``, ``rot_dim``, ``value_dim``, ``kv_rank``, ``q_rank``, ``scale``, ``position`` (a PartSpec
 of kind ``rope_interleaved``, or None), ``sink`` (bool), ``eps``.  Tensors: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, sink, o.
@@ -27,6 +29,7 @@ from typing import Mapping
 import torch
 
 from .. import ops
+from ..ops import attention as fast_attention
 from .attention_sloped import LARGEST_HEAD
 from .base import POSITIONS, BuildContext, Mixer, PagedTokens, WeightSpec, make, register_mixer
 from .spec import PartSpec
@@ -55,6 +58,7 @@ class LatentAttention(Mixer):
         if self.record > LARGEST_HEAD:
             raise ValueError(f"a record of {self.record} entries per token is above the kernel's limit of {LARGEST_HEAD}")
         self.q_head = self.head_dim + self.rot_dim
+        self.fast = self.dtype == torch.bfloat16 and fast_attention.latent_supported(self.record, self.kv_rank)
 
     def weights(self) -> dict[str, WeightSpec]:
         wanted = {"dq": WeightSpec((self.q_rank, self.hidden)), "dq.norm": WeightSpec((self.q_rank,), init="one_plus_normal"),
@@ -80,7 +84,10 @@ class LatentAttention(Mixer):
         return PagedTokens((1,), (self.record,), 0)
 
     def kernel_modules(self):
-        return [("heads_prepare", {}), ("attention_generic", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        modules = [("heads_prepare", {}), ("attention_generic", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        if self.fast:
+            modules.append(("attention_latent", {"HB_RECORD": self.record, "HB_VALUE": self.kv_rank}))
+        return modules
 
     @staticmethod
     def _batched(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -100,8 +107,14 @@ class LatentAttention(Mixer):
         plain = q.view(tokens, self.heads, self.q_head)[:, :, : self.head_dim].transpose(0, 1)
         q_lat = self._batched(plain, self.k_heads.to(q.dtype) if self.k_heads.dtype != q.dtype else self.k_heads, torch.float32)
         query = ops.latent_query(q, q_lat, self.heads, self.head_dim, self.rot_dim, inv_freq, self.rot_dims, step.positions)
-        attn = ops.attention_general(query, self.heads, 1, self.record, self.kv_rank, cache.kv, cache.block_table, step.token_row, step.positions,
-                                     cache.page_size, self.scale, sinks=self.sink, value_prefix=True)
+        if self.fast:
+            # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
+            longest = step.host.get("context_cap") or step.rows.longest_context
+            attn = fast_attention.attention_latent(query, self.heads, self.record, self.kv_rank, cache.kv, cache.block_table, step.row_start, step.positions,
+                                                   len(step.rows), int(step.rows.counts.max()), int(longest), self.scale, sinks=self.sink)
+        else:
+            attn = ops.attention_general(query, self.heads, 1, self.record, self.kv_rank, cache.kv, cache.block_table, step.token_row, step.positions,
+                                         cache.page_size, self.scale, sinks=self.sink, value_prefix=True)
         core = torch.empty((tokens, self.heads, self.value_dim), dtype=self.dtype, device=x.device)
         v_heads = self.v_heads.to(attn.dtype) if self.v_heads.dtype != attn.dtype else self.v_heads
         torch.bmm(attn.view(tokens, self.heads, self.kv_rank).transpose(0, 1), v_heads, out=core.transpose(0, 1))

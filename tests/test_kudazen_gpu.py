@@ -444,6 +444,67 @@ def test_a_key_far_away_among_hundreds_and_the_sink(folders, dtype):
     assert relative_error(plain.forward(config, weights, ids).numpy(), plain_logits(folders[name], ids)) > 100 * TOLERANCE["float32"]
 
 
+def _latent_attention_in_float(query, heads, record, value, cache, table, counts, firsts, page, scale, sinks):
+    """Every token alone, in float64: its keys are the records of positions 0 .. its own, its values their first entries."""
+    out, at = [], 0
+    for row, (count, first) in enumerate(zip(counts, firsts)):
+        context = first + count
+        records = torch.cat([cache[int(table[row, j // page]), 0, j % page][None] for j in range(context)]).double()
+        for i in range(count):
+            q = query[at].double().view(heads, record)
+            scores = (q @ records[: first + i + 1].T) * scale
+            if sinks is not None:
+                scores = torch.cat([scores, sinks.double()[:, None]], dim=1)
+            weights = torch.softmax(scores, dim=1)[:, : first + i + 1]
+            out.append((weights @ records[: first + i + 1, :value]).reshape(-1))
+            at += 1
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("heads,record,value,page", [(3, 32, 24, 8), (16, 96, 64, 16), (5, 208, 200, 4), (32, 48, 40, 8), (1, 16, 8, 8)])
+@pytest.mark.parametrize("with_sink", [False, True])
+def test_latent_attention_on_tensor_cores_against_float(heads, record, value, page, with_sink):
+    """The tensor-core kernel alone: rows of 1 to 70 tokens behind 0 to 300 cached ones over shuffled pages, in blocks of 16 and of 32
+    rows, with the keys whole and split 2, 3 and 7 ways (more shares than some rows have key tiles), with and without sinks; one key
+    far back is made to carry most of the weight of the last query."""
+    from hyperion_b200.ops import attention as fast
+
+    g = torch.Generator().manual_seed(heads * 1000 + record)
+    counts, firsts = [1, 70, 3, 1, 17], [300, 0, 129, 63, 64]
+    blocks = [-(-(f + c) // page) for c, f in zip(counts, firsts)]
+    pages = sum(blocks) + 5
+    order = torch.randperm(pages, generator=g).tolist()
+    table = torch.full((len(counts), max(blocks)), -1, dtype=torch.int32)
+    for row, n in enumerate(blocks):
+        for b in range(n):
+            table[row, b] = order.pop()
+    cache = (torch.randn(pages, 1, page, record, generator=g) * 0.7).to(torch.bfloat16)
+    tokens = sum(counts)
+    query = torch.randn(tokens, heads * record, generator=g).to(torch.bfloat16)
+    # the last row's last query points at the record of position 2 of its request, 78 places back
+    far = cache[int(table[4, 2 // page]), 0, 2 % page].float()
+    query[-1] = (3.0 * far / far.norm() * record ** 0.5).repeat(heads).to(torch.bfloat16)
+    sinks = (torch.randn(heads, generator=g) * 2.0) if with_sink else None
+    scale = 0.9 * record ** -0.5
+    want = _latent_attention_in_float(query, heads, record, value, cache, table, counts, firsts, page, scale, sinks)
+    starts = [0]
+    for c in counts:
+        starts.append(starts[-1] + c)
+    positions = torch.cat([torch.arange(c, dtype=torch.int32) + f for c, f in zip(counts, firsts)])
+    dev = torch.device("cuda")
+    args = (query.to(dev), heads, record, value, cache.to(dev), table.to(dev), torch.tensor(starts, dtype=torch.int32, device=dev), positions.to(dev), len(counts),
+            max(counts), max(c + f for c, f in zip(counts, firsts)), scale)
+    sinks_dev = sinks.to(dev) if with_sink else None
+    for shape in (None, (False, 1), (True, 1), (False, 2), (True, 3), (True, 7), (False, 7)):
+        got = fast.attention_latent(*args, sinks=sinks_dev, shape=shape).float().cpu().double()
+        error = ((got - want).norm(dim=1) / want.norm(dim=1).clamp_min(1e-3)).max().item()
+        assert error < 1.5e-2, (shape, error)
+    # the far key matters to the last query: without it the plain result is another
+    cache[int(table[4, 2 // page]), 0, 2 % page] = 0
+    other = _latent_attention_in_float(query, heads, record, value, cache, table, counts, firsts, page, scale, sinks)
+    assert ((other[-1] - want[-1]).norm() / want[-1].norm()).item() > 0.3
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_first_tokens_and_long_decoding(folders, name, dtype):
