@@ -739,10 +739,12 @@ def kudazen_kernels(size: dict, measured: dict) -> dict:
         tiles, items = fast.plan(fake_rows, fast.tile_tokens(heads, kv_heads, tile))
         seen_chunked = sum(min(p % chunk + 1, p + 1) for p in positions.tolist())
         seen_all = sum(p + 1 for p in positions.tolist())
+        per_position = (-slopes * 1.4426950408889634).contiguous()
         for label, window, bias, seen in (("attention.chunked_sloped", -chunk, by_distance, seen_chunked), ("qwen2.attention", 0, None, seen_all)):
             if len(tiles):
                 t_dev = torch.tensor(tiles, dtype=torch.int32, device=dev)
-                run = lambda: fast.attention_tiles(q, heads, cache, table, token_row, positions, t_dev, len(tiles) // 3, dim ** -0.5, window, attn, tile_size=tile, bias=bias)
+                run = lambda: fast.attention_tiles(q, heads, cache, table, token_row, positions, t_dev, len(tiles) // 3, dim ** -0.5, window, attn, tile_size=tile, bias=bias,
+                                                   bias_per_position=per_position if bias is not None else None)
             else:
                 i_dev = torch.tensor(items, dtype=torch.int32, device=dev)
                 splits = fast.choose_splits(len(items), heads, kv_heads, min(context, chunk + fast.KEY_TILE) if window else context)
@@ -767,8 +769,12 @@ def kudazen_kernels(size: dict, measured: dict) -> dict:
         sinks = torch.zeros(l_heads, device=dev)
         latent_flops = 2.0 * seen_all * l_heads * (record + rank)
         latent_bytes = rows * context * record * 2 + tokens * l_heads * (record + rank) * 2
+        l_shape = fast.choose_latent_shape(rows, max(counts), l_heads, context)
+        l_out = torch.empty(tokens, l_heads * rank, dtype=torch.bfloat16, device=dev)
+        l_space = torch.empty(tokens * l_heads * l_shape[1] * (rank + 2), dtype=torch.float32, device=dev)
         report(f"latent.attention/{shape}", timed(lambda: fast.attention_latent(query, l_heads, record, rank, l_cache, table, row_start, positions, rows, max(counts),
-                                                                              context, record ** -0.5, sinks=sinks), reps=5), latent_bytes, bf16_flops=latent_flops)
+                                                                              context, record ** -0.5, sinks=sinks, out=l_out, workspace=l_space, shape=l_shape), reps=5),
+               latent_bytes, bf16_flops=latent_flops)
         report(f"latent.attention_float_lanes/{shape}", timed(lambda: ops.attention_general(query, l_heads, 1, record, rank, l_cache, table, token_row, positions, page,
                                                                                           record ** -0.5, sinks=sinks, value_prefix=True), reps=3),
                latent_bytes, bf16_flops=latent_flops)

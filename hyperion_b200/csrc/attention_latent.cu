@@ -17,6 +17,7 @@
 // workspace; a second kernel merges the shares.  A row's result depends on the positions of the key tiles only, never on how the
 // request was cut into steps or on the rest of the batch.
 #include "common.cuh"
+#include <type_traits>
 
 #ifndef HB_RECORD
 #define HB_RECORD 576
@@ -94,7 +95,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_latent_kernel(const Late
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int brow = blockIdx.y, split = blockIdx.z;
     const int t0 = a.row_start[brow], count = a.row_start[brow + 1] - t0;
-    const int heads = a.heads, total = count * heads, base_f = blockIdx.x * M;
+    const int heads = a.heads, total = count * heads;
+    const int base_f = (gridDim.x - 1 - blockIdx.x) * M;  // a request's last rows see the most keys: their blocks start first
     if (base_f >= total) return;
     const int pos_first = a.positions[t0];
     const int hi = pos_first + (min(total, base_f + M) - 1) / heads;  // the last position any row of the block sees
@@ -117,17 +119,23 @@ __global__ void __launch_bounds__(THREADS, 1) attention_latent_kernel(const Late
 
     auto load_tile = [&](int tile, int buf) {  // a warp per key; keys past the block's last position are zeros
         __nv_bfloat16* dst0 = kbuf + (size_t)buf * BN * ROW;
-        for (int key = warp; key < BN; key += WARPS) {
-            const int j = tile * BN + key;
-            const __nv_bfloat16* src = nullptr;
+        // lane i looks up the page of the warp's i-th key, so the warp waits for one round of table reads, not for eight in a row
+        long long mine = -1;
+        if (lane < BN / WARPS) {
+            const int j = tile * BN + warp + lane * WARPS;
             if (j <= hi) {
                 const int block = j / a.page_size;
                 const int page = block < a.table_width ? table[block] : -1;
                 if (page < 0 || page >= a.pages) bad_page = true;
-                else src = a.cache + ((size_t)page * a.page_size + (j - block * a.page_size)) * RECORD;
+                else mine = ((long long)page * a.page_size + (j - block * a.page_size)) * RECORD;
             }
-            __nv_bfloat16* dst = dst0 + key * ROW;
-            if (src) {
+        }
+#pragma unroll
+        for (int i = 0; i < BN / WARPS; ++i) {
+            const long long offset = __shfl_sync(0xffffffffu, mine, i);
+            __nv_bfloat16* dst = dst0 + (warp + i * WARPS) * ROW;
+            if (offset >= 0) {
+                const __nv_bfloat16* src = a.cache + offset;
                 for (int c = lane; c < CHUNKS; c += 32) copy16_async(dst + c * 8, src + c * 8);
             } else {
                 for (int c = lane; c < CHUNKS; c += 32) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
@@ -170,42 +178,51 @@ __global__ void __launch_bounds__(THREADS, 1) attention_latent_kernel(const Late
         copies_commit();
         const __nv_bfloat16* kb = kbuf + (size_t)buf * BN * ROW;
 
-        // 1. scores of 16 rows against 8 * SN keys, two accumulators per key tile so that two chains of products are in flight
-        float s[2][SN][4];
+        // 1. scores of 16 rows against 8 * SN keys: the fragments of four contraction steps are fetched before their products are issued,
+        // and four sets of accumulators keep that many chains of products in flight
+        constexpr int U = 4;
+        float s[U][SN][4];
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
+        for (int c = 0; c < U; ++c)
 #pragma unroll
             for (int n = 0; n < SN; ++n)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[c][n][e] = 0.f;
         const uint32_t k_addr = shared_address(kb + (key0 + ((SN == 2) ? ((lane >> 4) << 3) : 0) + (lane & 7)) * ROW + ((lane >> 3) & 1) * 8);
-        auto score_step = [&](int ks, float (&into)[SN][4]) {
-            uint32_t qa[4];
-            ldmatrix_x4(qa, q_addr + ks * 32);
-            if constexpr (SN == 2) {
-                uint32_t kbf[4];
-                ldmatrix_x4(kbf, k_addr + ks * 32);
-                mma_bf16(into[0], qa, kbf[0], kbf[1]);
-                mma_bf16(into[SN - 1], qa, kbf[2], kbf[3]);
-            } else {
-                uint32_t kbf[2];
-                ldmatrix_x2(kbf, k_addr + ks * 32);
-                mma_bf16(into[0], qa, kbf[0], kbf[1]);
+        auto score_steps = [&](int ks0, auto count) {
+            constexpr int N = decltype(count)::value;
+            uint32_t qa[N][4], kf[N][4];
+#pragma unroll
+            for (int u = 0; u < N; ++u) {
+                ldmatrix_x4(qa[u], q_addr + (ks0 + u) * 32);
+                if constexpr (SN == 2) {
+                    ldmatrix_x4(kf[u], k_addr + (ks0 + u) * 32);
+                } else {
+                    uint32_t two[2];
+                    ldmatrix_x2(two, k_addr + (ks0 + u) * 32);
+                    kf[u][0] = two[0], kf[u][1] = two[1];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < N; ++u) {
+                mma_bf16(s[u][0], qa[u], kf[u][0], kf[u][1]);
+                if constexpr (SN == 2) mma_bf16(s[u][SN - 1], qa[u], kf[u][2], kf[u][3]);
             }
         };
-#pragma unroll 2
-        for (int ks = 0; ks + 1 < KSTEPS; ks += 2) {
-            score_step(ks, s[0]);
-            score_step(ks + 1, s[1]);
-        }
-        if constexpr (KSTEPS & 1) score_step(KSTEPS - 1, s[0]);
+#pragma unroll 1
+        for (int ks = 0; ks + U <= KSTEPS; ks += U) score_steps(ks, std::integral_constant<int, U>{});
+        if constexpr (KSTEPS % U) score_steps(KSTEPS - KSTEPS % U, std::integral_constant<int, KSTEPS % U>{});
+#pragma unroll
+        for (int n = 0; n < SN; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[0][n][e] = (s[0][n][e] + s[1][n][e]) + (s[2][n][e] + s[3][n][e]);
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int n = 0; n < SN; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = tile * BN + key0 + n * 8 + 2 * t + (e & 1);
-                const float v = (j <= row_pos[e >> 1]) ? (s[0][n][e] + s[1][n][e]) * a.scale_log2 : -INFINITY;
+                const float v = (j <= row_pos[e >> 1]) ? s[0][n][e] * a.scale_log2 : -INFINITY;
                 s[0][n][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }

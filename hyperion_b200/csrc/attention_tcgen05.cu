@@ -215,7 +215,8 @@ struct AttnArgs {
     int* status;
     int wide_stores;  // rows of the output start on 32-byte boundaries
     float cap_pre, cap_post;  // scale / cap and cap * log2(e) of a smooth cap on the scores (then scale_log2 is 1); cap_pre 0: none
-    const float* bias;  // [heads, bias_span] floats times log2(e), or null: a key n positions back adds bias[head, min(n, bias_span - 1)] to its score
+    const float* bias;  // [heads, bias_span] floats times log2(e), or null: a key n positions back adds bias[head, min(n, bias_span - 1)] to its score;
+                        // bias_span < 0: [heads], and a key n positions back adds n * bias[head]
     int bias_span;
     float bias_to_raw;  // 1 / scale_log2: a bias is added to the raw score as bias * bias_to_raw, so that the one scaling that follows stands
 };
@@ -230,7 +231,7 @@ struct AttnArgs {
 // tile all of them; with one block per item the longest item alone would set the kernel's time, now the items spread
 // evenly over the blocks. `work` = {items handed out beyond every block's first, blocks that have finished}: the block
 // that finishes last sets both back to zero for the next launch in the stream.
-template <bool BIASED>  // a bias by distance on the scores: a kernel of its own, so that the other keeps its registers
+template <int BIASED>  // a bias by distance on the scores (1: a table, 2: a number per head times the distance): kernels of their own, so that the others keep their registers
 __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
                                                                   const AttnArgs a,
                                                                   const int* __restrict__ tiles, int n_work_tiles, int ys, int gc, int head_chunks,
@@ -516,7 +517,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
                     // behind every row of the warp takes it as a shift of the whole tile (nothing per score); only the tiles
                     // near the diagonal look their scores' biases up.
                     float shift = 0.f;
-                    if (BIASED) {
+                    if constexpr (BIASED == 2) {  // a bias that is linear in the distance: one number per head, nothing to look up
+                        const float per = a.bias[it.first_head + (row_valid ? hh : 0)];
+                        shift = per * (float)(hi - tile_base);  // the tile's first key; key i of the tile is i positions nearer
+                        const float step = -per * a.bias_to_raw;
+#pragma unroll
+                        for (int i = 0; i < BN; ++i) s[i] = fmaf(step, (float)i, s[i]);
+                    } else if constexpr (BIASED == 1) {
                         const float* mine = a.bias + (size_t)(it.first_head + (row_valid ? hh : 0)) * a.bias_span;
                         const int nearest = hi - (tile_base + BN - 1);  // the distance of the tile's last key
                         if (__all_sync(0xffffffffu, nearest >= a.bias_span - 1)) {
@@ -659,14 +666,15 @@ constexpr size_t SMEM_BYTES = SMEM_USED > 120 * 1024 ? SMEM_USED : 120 * 1024;
 // 256 / min(group, 256) tokens.
 HB_EXPORT int hb_attention_tc_tile_rows() { return ROWS; }
 
-// bias [heads, bias_span] float (optional), already times log2(e): see AttnArgs.  Not together with a cap.
+// bias [heads, bias_span] float (optional), already times log2(e), or with bias_span < 0 one number per head that multiplies the
+// distance: see AttnArgs.  Not together with a cap.
 HB_EXPORT int hb_attention_tc_tiles_biased(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                     int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int n_tokens,
                                     int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window,
                                     const float* bias, int bias_span, int* status, int* work, cudaStream_t stream) {
     (void)token_row;
     if (!work) return HB_BAD_ARGUMENT;
-    if (bias && (bias_span <= 0 || softcap > 0.f)) return HB_BAD_ARGUMENT;
+    if (bias && (bias_span == 0 || softcap > 0.f)) return HB_BAD_ARGUMENT;
     if (n_tiles <= 0) return 0;
     if (n_tokens <= 0) return HB_BAD_ARGUMENT;
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
@@ -701,8 +709,9 @@ HB_EXPORT int hb_attention_tc_tiles_biased(const void* q, int q_stride, void* ou
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -713,10 +722,13 @@ HB_EXPORT int hb_attention_tc_tiles_biased(const void* q, int q_stride, void* ou
     const long long items = (long long)n_tiles * kv_heads * head_chunks;
     if (items > 0x7fffffffLL) return HB_UNSUPPORTED_SIZE;
     const int blocks = (int)(items < (long long)sms ? items : (long long)sms);
-    if (bias)
-        return launch_after_previous(attention_tc_kernel<true>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles,
+    if (bias && bias_span < 0)
+        return launch_after_previous(attention_tc_kernel<2>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles,
                                      kv_heads * head_chunks, gc, head_chunks, work);
-    return launch_after_previous(attention_tc_kernel<false>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
+    if (bias)
+        return launch_after_previous(attention_tc_kernel<1>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles,
+                                     kv_heads * head_chunks, gc, head_chunks, work);
+    return launch_after_previous(attention_tc_kernel<0>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
                                  head_chunks, work);
 }
 

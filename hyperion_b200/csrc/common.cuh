@@ -134,3 +134,21 @@ __host__ __device__ __forceinline__ int first_seen(int pos, int window) {
     if (window < 0) return pos >= 0 ? pos - pos % (-window) : 0;
     return 0;
 }
+
+// Four consecutive elements as floats, by one 16-byte (float) or 8-byte (bfloat16) access; p is aligned to that.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&x.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+    v[0] = __low2float(lo), v[1] = __high2float(lo), v[2] = __low2float(hi), v[3] = __high2float(hi);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 x;
+    x.x = *reinterpret_cast<const uint32_t*>(&lo), x.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = x;
+}

@@ -883,16 +883,90 @@ __global__ void __launch_bounds__(256) add_group_rmsnorm_kernel(float* __restric
     }
 }
 
+// The same with four columns per access, for parts that are a multiple of four columns: a lane adds its own columns in order, then the
+// butterfly, so the sums still have one shape whatever the launch.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) add_group_rmsnorm4_kernel(float* __restrict__ h, const TD* __restrict__ d1, const TD* __restrict__ d2,
+                                                                 const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows,
+                                                                 int hidden, int groups, float eps, int write_h) {
+    __shared__ float inv[64];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* hrow = h + (size_t)s * hidden;
+    const TD* a = d1 ? d1 + (size_t)s * hidden : nullptr;
+    const TD* b = d2 ? d2 + (size_t)s * hidden : nullptr;
+    const int part = hidden / groups, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int g = warp; g < groups; g += warps) {
+        float sum = 0.f;
+#pragma unroll 4
+        for (int i = g * part + lane * 4; i < (g + 1) * part; i += 128) {
+            float v[4], x[4];
+            load4(hrow + i, v);
+            if (a) {
+                load4(a + i, x);
+                if (b) {
+                    float y[4];
+                    load4(b + i, y);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[e] += y[e];
+                }
+            } else if (b) {
+                load4(b + i, x);
+            }
+            if (a || b) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] += x[e];
+                if (write_h) store4(hrow + i, v);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum = fmaf(v[e], v[e], sum);
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) inv[g] = 1.0f / sqrtf(sum / (float)part + eps);
+    }
+    __syncthreads();
+    TO* orow = out + (size_t)r * hidden;
+#pragma unroll 2
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+        float v[4], w[4];
+        load4(hrow + i, v);
+        if (!write_h && (a || b)) {
+            float x[4];
+            if (a) {
+                load4(a + i, x);
+                if (b) {
+                    float y[4];
+                    load4(b + i, y);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[e] += y[e];
+                }
+            } else {
+                load4(b + i, x);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] += x[e];
+        }
+        load4(weight + i, w);
+        const float scale = inv[i / part];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = v[e] * scale * w[e];
+        store4(orow + i, v);
+    }
+}
+
 HB_EXPORT int hb_add_group_rmsnorm(float* h, const void* d1, const void* d2, int delta_is_bf16, const float* weight, void* out, int out_is_bf16,
                                    const int* rows, int n_rows, int hidden, int groups, float eps, int write_h, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (hidden <= 0 || groups <= 0 || groups > 64 || hidden % groups) return HB_UNSUPPORTED_SIZE;
     const int threads = groups >= 8 ? 256 : (groups * 32 < 128 ? 128 : groups * 32);
-#define HB_GROUP_NORM(TD, TO) add_group_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h)
-    if (delta_is_bf16 && out_is_bf16) HB_GROUP_NORM(__nv_bfloat16, __nv_bfloat16);
-    else if (delta_is_bf16) HB_GROUP_NORM(__nv_bfloat16, float);
-    else if (out_is_bf16) HB_GROUP_NORM(float, __nv_bfloat16);
-    else HB_GROUP_NORM(float, float);
+    const bool by_four = (hidden / groups) % 4 == 0 && (((uintptr_t)h | (uintptr_t)d1 | (uintptr_t)d2 | (uintptr_t)weight | (uintptr_t)out) % 16) == 0;
+#define HB_GROUP_NORM(TD, TO)                                                                                                                          \
+    if (by_four) add_group_rmsnorm4_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h); \
+    else add_group_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h)
+    if (delta_is_bf16 && out_is_bf16) { HB_GROUP_NORM(__nv_bfloat16, __nv_bfloat16); }
+    else if (delta_is_bf16) { HB_GROUP_NORM(__nv_bfloat16, float); }
+    else if (out_is_bf16) { HB_GROUP_NORM(float, __nv_bfloat16); }
+    else { HB_GROUP_NORM(float, float); }
 #undef HB_GROUP_NORM
     return launch_status();
 }
@@ -911,16 +985,36 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gate_up, T* __restrict_
     }
 }
 
+template <typename T>
+__global__ void clamped_glu4_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, float limit, float slope) {
+    const int t = blockIdx.y;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4; i < inter; i += gridDim.x * blockDim.x * 4) {
+        const size_t at = (size_t)t * 2 * inter + i;
+        float g[4], u[4];
+        load4(gate_up + at, g);
+        load4(gate_up + at + inter, u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float gg = fminf(g[e], limit), uu = fminf(fmaxf(u[e], -limit), limit);
+            g[e] = gg / (1.0f + expf(-slope * gg)) * (uu + 1.0f);
+        }
+        store4(out + (size_t)t * inter + i, g);
+    }
+}
+
 HB_EXPORT int hb_clamped_glu(const void* gate_up, void* out, int is_bf16, int tokens, int inter, float limit, float slope, cudaStream_t stream) {
     if (tokens <= 0 || inter <= 0) return 0;
+    const bool by_four = inter % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) % 16) == 0;
     for (int first = 0; first < tokens; first += 65535) {
         const int count = tokens - first < 65535 ? tokens - first : 65535;
-        const int across = (inter + 255) / 256;
+        const int across = by_four ? (inter / 4 + 255) / 256 : (inter + 255) / 256;
         const dim3 grid(across < 16 ? across : 16, count);
-        if (is_bf16)
-            clamped_glu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gate_up + (size_t)first * 2 * inter, (__nv_bfloat16*)out + (size_t)first * inter, inter, limit, slope);
-        else
-            clamped_glu_kernel<<<grid, 256, 0, stream>>>((const float*)gate_up + (size_t)first * 2 * inter, (float*)out + (size_t)first * inter, inter, limit, slope);
+#define HB_CLAMPED(T)                                                                                                                              \
+    if (by_four) clamped_glu4_kernel<<<grid, 256, 0, stream>>>((const T*)gate_up + (size_t)first * 2 * inter, (T*)out + (size_t)first * inter, inter, limit, slope); \
+    else clamped_glu_kernel<<<grid, 256, 0, stream>>>((const T*)gate_up + (size_t)first * 2 * inter, (T*)out + (size_t)first * inter, inter, limit, slope)
+        if (is_bf16) { HB_CLAMPED(__nv_bfloat16); }
+        else { HB_CLAMPED(float); }
+#undef HB_CLAMPED
     }
     return launch_status();
 }

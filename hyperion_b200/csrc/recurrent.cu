@@ -483,6 +483,34 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ x, int x_stride, co
     }
 }
 
+// Four columns per access, for rows of a multiple of four columns that start on 16-byte boundaries.
+template <typename T>
+__global__ void token_shift_mix4_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ mu, int n_mix, const float* __restrict__ state,
+                                        size_t slot_stride, int state_off, const int* __restrict__ slots, const int* __restrict__ token_row,
+                                        const int* __restrict__ row_start, T* __restrict__ out, int tokens, int hidden) {
+    const int t = blockIdx.x;
+    const int row = token_row[t];
+    const bool first = t == row_start[row];
+    const T* now = x + (size_t)t * x_stride;
+    const T* before = x + (size_t)(t - 1) * x_stride;
+    const float* kept = state + (size_t)slots[row] * slot_stride + state_off;
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+        float h[4], d[4];
+        load4(now + i, h);
+        if (first) load4(kept + i, d);
+        else load4(before + i, d);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d[e] -= h[e];
+        for (int m = 0; m < n_mix; ++m) {
+            float w[4], v[4];
+            load4(mu + (size_t)m * hidden + i, w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = fmaf(d[e], w[e], h[e]);
+            store4(out + ((size_t)m * tokens + t) * hidden + i, v);
+        }
+    }
+}
+
 template <typename T>
 __global__ void token_shift_keep_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state, size_t slot_stride, int state_off,
                                         const int* __restrict__ slots, const int* __restrict__ row_start, int hidden) {
@@ -504,6 +532,17 @@ HB_EXPORT int hb_token_shift_mix(const void* x, int is_bf16, int x_stride, const
     if (tokens <= 0) return 0;
     if (hidden <= 0 || n_mix <= 0) return HB_UNSUPPORTED_SIZE;
     const int threads = hidden >= 1024 ? 256 : 128;
+    const bool by_four = hidden % 4 == 0 && x_stride % 8 == 0 && slot_stride % 4 == 0 && state_off % 4 == 0 &&
+                         (((uintptr_t)x | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)out) % 16) == 0;
+    if (by_four) {
+        if (is_bf16)
+            token_shift_mix4_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, mu, n_mix, state, (size_t)slot_stride, state_off, slots, token_row,
+                                                                    row_start, (__nv_bfloat16*)out, tokens, hidden);
+        else
+            token_shift_mix4_kernel<<<tokens, threads, 0, stream>>>((const float*)x, x_stride, mu, n_mix, state, (size_t)slot_stride, state_off, slots, token_row, row_start,
+                                                                    (float*)out, tokens, hidden);
+        return launch_status();
+    }
     if (is_bf16)
         token_shift_mix_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, mu, n_mix, state, (size_t)slot_stride, state_off, slots, token_row,
                                                                row_start, (__nv_bfloat16*)out, tokens, hidden);

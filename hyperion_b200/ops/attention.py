@@ -109,12 +109,23 @@ def _common(q, out, cache, block_table, token_row, positions):
 
 
 def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out, tile_size: int = TILE_ROWS,
-                    softcap: float = 0.0, bias=None):
+                    softcap: float = 0.0, bias=None, bias_per_position=None):
     """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 256 for the tcgen05 kernel).
     ``softcap`` > 0: scores become cap * tanh(score / cap) before the softmax.  ``bias`` [heads, span] float, times log2(e):
-    the score of a key n positions back takes ``bias[head, min(n, span - 1)]``."""
+    the score of a key n positions back takes ``bias[head, min(n, span - 1)]``.  ``bias_per_position`` [heads] float, times log2(e):
+    where the bias is n times a number per head, the tcgen05 kernel computes it instead of looking it up (the others take ``bias``)."""
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
+    if bias_per_position is not None and uses_tcgen05(head_dim, page_size) and tile_size == TC_TILE_ROWS:
+        require_cuda(bias_per_position)
+        if bias_per_position.dtype != torch.float32 or bias_per_position.numel() != heads or not bias_per_position.is_contiguous():
+            raise KernelError("attention: the bias per position is a dense float32 vector with one entry per head")
+        check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles_biased(
+            ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
+            ptr(positions), ptr(tiles), i32(n_tiles), i32(q.shape[0]), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages),
+            f32(scale), f32(softcap or 0.0), i32(window or 0), ptr(bias_per_position), i32(-1), ptr(status_word(q.device)), ptr(work_counters(q.device)),
+            stream_ptr()), "attention_tiles")
+        return
     if bias is not None:
         require_cuda(bias)
         bias_ptr, span = _bias_arguments(bias, heads, head_dim, page_size)

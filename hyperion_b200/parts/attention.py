@@ -138,8 +138,9 @@ class GroupedQueryAttention(Mixer):
             return int((rows.positions[short] + rows.counts[short]).max())
         return max(row.position + row.count for row in rows if row.count <= fast_attention.TOKEN_SHAPE_MAX)
 
-    def _attend_fast(self, qkv, step, cache, out=None, bias=None):
-        """``out``: a [tokens, >= heads * head_dim] view to write to; ``bias``: a table by distance (``ops.attention.attention_tiles``)."""
+    def _attend_fast(self, qkv, step, cache, out=None, bias=None, bias_per_position=None):
+        """``out``: a [tokens, >= heads * head_dim] view to write to; ``bias``: a table by distance, ``bias_per_position``: the same bias
+        as one number per head where it is linear in the distance (``ops.attention.attention_tiles``)."""
         if out is None:
             out = torch.empty((step.n_tokens, self.heads * self.head_dim), dtype=self.dtype, device=qkv.device)
         size = fast_attention.tile_rows(self.head_dim, step.host.get("page_size"))
@@ -147,7 +148,8 @@ class GroupedQueryAttention(Mixer):
         n_tiles, n_items = step.host.get(key, 0), step.host.get("attn_items", 0)
         if n_tiles:
             fast_attention.attention_tiles(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
-                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size, softcap=self.softcap, bias=bias)
+                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size, softcap=self.softcap, bias=bias,
+                                           bias_per_position=bias_per_position)
         if n_items:
             # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
             longest = step.host.get("context_cap") or self._longest_short_row(step.rows)

@@ -12,7 +12,8 @@ Per step: one product to [q | k | v] kept in float; one kernel (``csrc/heads_pre
 and values to their pages and the queries to a dense buffer; attention of every token over its request's pages; the output
 projection.  In bfloat16, with keys and values of one size that is a multiple of 64 and chunks of at most ``LONGEST_TABLE``
 positions, attention runs in the tensor-core kernels of the package's other attentions (tcgen05 tiles for prompt portions, split
-keys for decoded tokens): inside a chunk no distance exceeds the chunk, so the slopes become a table by distance, the chunk is
+keys for decoded tokens): inside a chunk no distance exceeds the chunk, so the slopes become a table by distance (the tcgen05
+kernel computes slope times distance itself), the chunk is
 those kernels' window argument with a negative sign, and the head's factor multiplies its query (in float, before the query's one
 rounding).  Everything else, and float32, runs in ``csrc/attention_generic.cu`` (scores, factor, slope and softmax in float).
 
@@ -68,10 +69,11 @@ class SlopedAttention(Mixer):
         self.window, self.softcap = -self.chunk, 0.0  # as the tensor-core kernels take them: a negative window is a chunk
         self.fast = (self.dtype == torch.bfloat16 and self.value_dim == self.head_dim and self.head_dim % 64 == 0 and fast_attention.supported(self.head_dim)
                      and (self.slopes is None or 0 < self.chunk <= LONGEST_TABLE))
-        self.by_distance_log2 = None
+        self.by_distance_log2 = self.per_position_log2 = None
         if self.fast and self.slopes is not None:  # [heads, chunk]: minus slope times distance, in the base-2 units of those kernels' softmax
             distance = torch.arange(self.chunk, dtype=torch.float32, device=build.device)
             self.by_distance_log2 = (-(self.slopes[:, None] * distance[None, :]) * math.log2(math.e)).contiguous()
+            self.per_position_log2 = (-self.slopes * math.log2(math.e)).contiguous()  # [heads]: kernels that compute the bias take this
 
     def weights(self) -> dict[str, WeightSpec]:
         wanted = {"q": WeightSpec((self.q_width, self.hidden)), "k": WeightSpec((self.k_width, self.hidden)), "v": WeightSpec((self.v_width, self.hidden)),
@@ -116,7 +118,7 @@ class SlopedAttention(Mixer):
                                q_out=q, cache=cache.kv, block_table=cache.block_table, token_row=step.token_row, page_size=cache.page_size,
                                v_unit_eps=self.eps if self.value_unit_rms else None, q_head_scale=self.temp if fast else None)
         if fast:
-            attn = self._attend_fast(q, step, cache, bias=self.by_distance_log2)
+            attn = self._attend_fast(q, step, cache, bias=self.by_distance_log2, bias_per_position=self.per_position_log2)
             return ops.linear(attn, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
         attn = ops.attention_general(q, self.heads, self.kv_heads, self.head_dim, self.value_dim, cache.kv, cache.block_table, step.token_row, step.positions,
                                      cache.page_size, self.scale, head_scale=self.temp, slopes=self.slopes, chunk=self.chunk)
