@@ -178,8 +178,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_latent_kernel(const Late
         copies_commit();
         const __nv_bfloat16* kb = kbuf + (size_t)buf * BN * ROW;
 
-        // 1. scores of 16 rows against 8 * SN keys: the fragments of four contraction steps are fetched before their products are issued,
-        // and four sets of accumulators keep that many chains of products in flight
+        // 1. scores of 16 rows against 8 * SN keys: fragments are fetched ahead of the products that use them, and four sets of accumulators
+        // keep that many chains of products in flight
         constexpr int U = 4;
         float s[U][SN][4];
 #pragma unroll
@@ -189,29 +189,26 @@ __global__ void __launch_bounds__(THREADS, 1) attention_latent_kernel(const Late
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[c][n][e] = 0.f;
         const uint32_t k_addr = shared_address(kb + (key0 + ((SN == 2) ? ((lane >> 4) << 3) : 0) + (lane & 7)) * ROW + ((lane >> 3) & 1) * 8);
-        auto score_steps = [&](int ks0, auto count) {
-            constexpr int N = decltype(count)::value;
-            uint32_t qa[N][4], kf[N][4];
+        constexpr int AHEAD = 3;  // a step's fragments are asked for three steps before its products are issued
+        uint32_t qa[AHEAD + 1][4], kf[AHEAD + 1][4];
 #pragma unroll
-            for (int u = 0; u < N; ++u) {
-                ldmatrix_x4(qa[u], q_addr + (ks0 + u) * 32);
+        for (int ks = 0; ks < KSTEPS + AHEAD; ++ks) {
+            if (ks < KSTEPS) {
+                ldmatrix_x4(qa[ks % (AHEAD + 1)], q_addr + ks * 32);
                 if constexpr (SN == 2) {
-                    ldmatrix_x4(kf[u], k_addr + (ks0 + u) * 32);
+                    ldmatrix_x4(kf[ks % (AHEAD + 1)], k_addr + ks * 32);
                 } else {
                     uint32_t two[2];
-                    ldmatrix_x2(two, k_addr + (ks0 + u) * 32);
-                    kf[u][0] = two[0], kf[u][1] = two[1];
+                    ldmatrix_x2(two, k_addr + ks * 32);
+                    kf[ks % (AHEAD + 1)][0] = two[0], kf[ks % (AHEAD + 1)][1] = two[1];
                 }
             }
-#pragma unroll
-            for (int u = 0; u < N; ++u) {
-                mma_bf16(s[u][0], qa[u], kf[u][0], kf[u][1]);
-                if constexpr (SN == 2) mma_bf16(s[u][SN - 1], qa[u], kf[u][2], kf[u][3]);
+            if (ks >= AHEAD) {
+                const int at = ks - AHEAD;
+                mma_bf16(s[at % U][0], qa[at % (AHEAD + 1)], kf[at % (AHEAD + 1)][0], kf[at % (AHEAD + 1)][1]);
+                if constexpr (SN == 2) mma_bf16(s[at % U][SN - 1], qa[at % (AHEAD + 1)], kf[at % (AHEAD + 1)][2], kf[at % (AHEAD + 1)][3]);
             }
-        };
-#pragma unroll 1
-        for (int ks = 0; ks + U <= KSTEPS; ks += U) score_steps(ks, std::integral_constant<int, U>{});
-        if constexpr (KSTEPS % U) score_steps(KSTEPS - KSTEPS % U, std::integral_constant<int, KSTEPS % U>{});
+        }
 #pragma unroll
         for (int n = 0; n < SN; ++n)
 #pragma unroll
@@ -276,21 +273,27 @@ __global__ void __launch_bounds__(THREADS, 1) attention_latent_kernel(const Late
 #pragma unroll
                 for (int i = 0; i < MT; ++i) ldmatrix_x4(pa[i], p_addr + (i * 16 * PROW + kk * 16) * 2);
                 const __nv_bfloat16* vrow = kb + (kk * 16 + (lane & 15)) * ROW + n_first * 8;
+                // all of this step's value fragments first, then its products
+                uint32_t vb[(NTW + 1) / 2][4];
 #pragma unroll
                 for (int n = 0; n < NTW; n += 2) {
                     if (n + 1 < n_here) {
-                        uint32_t vb[4];
-                        ldmatrix_x4_trans(vb, shared_address(vrow + n * 8 + (lane >> 4) * 8));
-#pragma unroll
-                        for (int i = 0; i < MT; ++i) {
-                            mma_bf16(acc[i][n], pa[i], vb[0], vb[1]);
-                            if (n + 1 < NTW) mma_bf16(acc[i][n + 1 < NTW ? n + 1 : n], pa[i], vb[2], vb[3]);
-                        }
+                        ldmatrix_x4_trans(vb[n / 2], shared_address(vrow + n * 8 + (lane >> 4) * 8));
                     } else if (n < n_here) {
-                        uint32_t vb[2];
-                        ldmatrix_x2_trans(vb, shared_address(vrow + n * 8));
+                        uint32_t two[2];
+                        ldmatrix_x2_trans(two, shared_address(vrow + n * 8));
+                        vb[n / 2][0] = two[0], vb[n / 2][1] = two[1];
+                    }
+                }
 #pragma unroll
-                        for (int i = 0; i < MT; ++i) mma_bf16(acc[i][n], pa[i], vb[0], vb[1]);
+                for (int n = 0; n < NTW; n += 2) {
+                    if (n < n_here) {
+#pragma unroll
+                        for (int i = 0; i < MT; ++i) mma_bf16(acc[i][n], pa[i], vb[n / 2][0], vb[n / 2][1]);
+                    }
+                    if (n + 1 < n_here && n + 1 < NTW) {
+#pragma unroll
+                        for (int i = 0; i < MT; ++i) mma_bf16(acc[i][n + 1 < NTW ? n + 1 : n], pa[i], vb[n / 2][2], vb[n / 2][3]);
                     }
                 }
             }

@@ -883,23 +883,27 @@ __global__ void __launch_bounds__(256) add_group_rmsnorm_kernel(float* __restric
     }
 }
 
-// The same with four columns per access, for parts that are a multiple of four columns: a lane adds its own columns in order, then the
-// butterfly, so the sums still have one shape whatever the launch.
+// The same with four columns per access, for parts that are a multiple of four columns.  When the block has more warps than the row
+// has groups, a group's columns are cut into equal runs, one per warp, and the runs' sums are added in order: the sums have one shape
+// for a given row length and number of groups, whatever else is in the launch.
 template <typename TD, typename TO>
-__global__ void __launch_bounds__(256) add_group_rmsnorm4_kernel(float* __restrict__ h, const TD* __restrict__ d1, const TD* __restrict__ d2,
+__global__ void __launch_bounds__(512) add_group_rmsnorm4_kernel(float* __restrict__ h, const TD* __restrict__ d1, const TD* __restrict__ d2,
                                                                  const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows,
                                                                  int hidden, int groups, float eps, int write_h) {
-    __shared__ float inv[64];
+    __shared__ float inv[64], partial[64];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* hrow = h + (size_t)s * hidden;
     const TD* a = d1 ? d1 + (size_t)s * hidden : nullptr;
     const TD* b = d2 ? d2 + (size_t)s * hidden : nullptr;
     const int part = hidden / groups, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    for (int g = warp; g < groups; g += warps) {
+    const int runs = groups < warps ? warps / groups : 1, quads = part / 4, per_run = (quads + runs - 1) / runs;
+    for (int item = warp; item < groups * runs; item += warps) {
+        const int g = item / runs, k = item - g * runs;
+        const int lo = g * part + min(quads, k * per_run) * 4, hi = g * part + min(quads, (k + 1) * per_run) * 4;
         float sum = 0.f;
 #pragma unroll 4
-        for (int i = g * part + lane * 4; i < (g + 1) * part; i += 128) {
+        for (int i = lo + lane * 4; i < hi; i += 128) {
             float v[4], x[4];
             load4(hrow + i, v);
             if (a) {
@@ -922,7 +926,13 @@ __global__ void __launch_bounds__(256) add_group_rmsnorm4_kernel(float* __restri
             for (int e = 0; e < 4; ++e) sum = fmaf(v[e], v[e], sum);
         }
         sum = warp_sum(sum);
-        if (lane == 0) inv[g] = 1.0f / sqrtf(sum / (float)part + eps);
+        if (lane == 0) partial[item] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x < groups) {
+        float sum = 0.f;
+        for (int k = 0; k < runs; ++k) sum += partial[threadIdx.x * runs + k];
+        inv[threadIdx.x] = 1.0f / sqrtf(sum / (float)part + eps);
     }
     __syncthreads();
     TO* orow = out + (size_t)r * hidden;
@@ -961,7 +971,7 @@ HB_EXPORT int hb_add_group_rmsnorm(float* h, const void* d1, const void* d2, int
     const int threads = groups >= 8 ? 256 : (groups * 32 < 128 ? 128 : groups * 32);
     const bool by_four = (hidden / groups) % 4 == 0 && (((uintptr_t)h | (uintptr_t)d1 | (uintptr_t)d2 | (uintptr_t)weight | (uintptr_t)out) % 16) == 0;
 #define HB_GROUP_NORM(TD, TO)                                                                                                                          \
-    if (by_four) add_group_rmsnorm4_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h); \
+    if (by_four) add_group_rmsnorm4_kernel<TD, TO><<<n_rows, hidden >= 4096 ? 512 : 256, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h); \
     else add_group_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)d1, (const TD*)d2, weight, (TO*)out, rows, hidden, groups, eps, write_h)
     if (delta_is_bf16 && out_is_bf16) { HB_GROUP_NORM(__nv_bfloat16, __nv_bfloat16); }
     else if (delta_is_bf16) { HB_GROUP_NORM(__nv_bfloat16, float); }
