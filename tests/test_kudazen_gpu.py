@@ -92,6 +92,8 @@ ALONE = {
     "attention_open": document(40, 61, [layer(attention(3, 3, 8, 12, 0.6))], groups=1),
     "latent": document(48, 97, [layer(latent(3, 12, 8, 20, 24, 24, 0.12))], groups=2),
     "latent_wide": document(40, 61, [layer(latent(1, 136, 24, 72, 200, 8, 0.1))], groups=5),
+    # a record of 26 entries is no multiple of 16: in bfloat16 too this one stays in the kernel with float lanes
+    "latent_odd": document(40, 61, [layer(latent(2, 10, 6, 12, 20, 16, 0.25))], groups=1),
     "wkv": document(48, 97, [layer(wkv(3, 20, 5))], groups=2),
     "wkv_wide": document(40, 61, [layer(wkv(1, 136, 2))], groups=1),
     "dense": document(48, 97, [layer(wkv(1, 4, 1), dense(100, 0.7))], groups=6),
@@ -252,6 +254,8 @@ def test_one_layer_of_each_kind(folders, name, dtype):
     ids = ids_for(3, 75, vocab)
     want = plain_logits(folders[name], ids)
     engine = engine_for(folders[name], dtype, page_size=8)
+    if name.startswith("latent"):  # which kernel runs: the tensor cores in bfloat16 when the record's size allows
+        assert engine.model.layers[0].mixer.fast == (dtype == "bfloat16" and name != "latent_odd")
     assert_close(run_cut(engine, "w", ids, [len(ids)]), want, dtype, "whole")
     assert_close(run_cut(engine, "p", ids, [5, 2, 1, 9]), want, dtype, "portions")
 
