@@ -1028,3 +1028,32 @@ HB_EXPORT int hb_clamped_glu(const void* gate_up, void* out, int is_bf16, int to
     }
     return launch_status();
 }
+
+// ---------------------------------------------------------------- GELU in its exact form, and a scale in place
+// out = 0.5 z (1 + erf(z / sqrt(2))), in float, rounded once.  hb_scale_rows: x <- x * scale over a dense float tensor.
+template <typename T>
+__global__ void gelu_erf_kernel(const T* __restrict__ x, T* __restrict__ out, size_t count) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const float z = to_float(x[i]);
+        out[i] = from_float<T>(0.5f * z * (1.f + erff(z * 0.7071067811865476f)));
+    }
+}
+
+HB_EXPORT int hb_gelu_erf(const void* x, void* out, int is_bf16, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+    if (is_bf16) gelu_erf_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)count);
+    else gelu_erf_kernel<<<blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)count);
+    return launch_status();
+}
+
+__global__ void scale_rows_kernel(float* __restrict__ x, float scale, size_t count) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) x[i] *= scale;
+}
+
+HB_EXPORT int hb_scale_rows(float* x, float scale, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+    scale_rows_kernel<<<blocks, 256, 0, stream>>>(x, scale, (size_t)count);
+    return launch_status();
+}

@@ -434,3 +434,55 @@ HB_EXPORT int hb_latent_query(const void* q, int is_bf16, int tokens, int q_stri
                                                           kv_rank, inv_freq, positions, (float*)out, out_stride);
     return launch_status();
 }
+
+// ---------------------------------------------------------------- a rotation of heads in place
+// Every head of the columns col0 .. col0 + heads * head_dim of a row turns by sign * position: within a head's first rot_dims entries,
+// entry i with entry i + rot_dims / 2 (rot_half) or entry 2i with 2i + 1, pair i by the angle sign * position * inv_freq[i]; the rest
+// of the head stays.  Values that are cached rotated by their own position and results that are turned back by the query's position
+// (sign = -1) both pass through here.  The angle, its sine and cosine and the products are float; one rounding at the store.
+namespace {
+constexpr int ROTATE_THREADS = 256, ROTATE_PAIRS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(ROTATE_THREADS) rotate_heads_kernel(T* x, int stride, int col0, int heads, int head_dim, int rot_dims, int rot_half,
+                                                                      const float* __restrict__ inv_freq, const int* __restrict__ positions, float sign) {
+    __shared__ float cs[ROTATE_PAIRS], sn[ROTATE_PAIRS];
+    const int t = blockIdx.x, pairs = rot_dims / 2;
+    const float pos = (float)positions[t];
+    const bool tabled = pairs <= ROTATE_PAIRS;
+    if (tabled) {
+        for (int i = threadIdx.x; i < pairs; i += ROTATE_THREADS) {
+            float s, c;
+            sincosf(pos * inv_freq[i], &s, &c);
+            cs[i] = c;
+            sn[i] = sign * s;
+        }
+        __syncthreads();
+    }
+    T* row = x + (size_t)t * stride + col0;
+    for (int item = blockIdx.y * ROTATE_THREADS + threadIdx.x; item < heads * pairs; item += gridDim.y * ROTATE_THREADS) {
+        const int head = item / pairs, i = item % pairs;
+        const int a = rot_half ? i : 2 * i, b = rot_half ? i + pairs : 2 * i + 1;
+        T* p = row + (size_t)head * head_dim;
+        float s, c;
+        if (tabled) { c = cs[i]; s = sn[i]; }
+        else { sincosf(pos * inv_freq[i], &s, &c); s *= sign; }
+        const float u = to_float(p[a]), v = to_float(p[b]);
+        p[a] = from_float<T>(u * c - v * s);
+        p[b] = from_float<T>(v * c + u * s);
+    }
+}
+}  // namespace
+
+HB_EXPORT int hb_rotate_heads(void* x, int is_bf16, int tokens, int stride, int col0, int heads, int head_dim, int rot_dims, int rot_half,
+                              const float* inv_freq, const int* positions, float sign, cudaStream_t stream) {
+    if (tokens <= 0 || heads <= 0 || rot_dims <= 0) return 0;
+    if (head_dim <= 0 || rot_dims > head_dim || (rot_dims & 1) || !inv_freq || !positions) return HB_UNSUPPORTED_SIZE;
+    const int items = heads * (rot_dims / 2);
+    int parts = tokens >= 512 ? 1 : (items + ROTATE_THREADS - 1) / ROTATE_THREADS;  // few tokens: a token's pairs over several blocks
+    parts = parts < 1 ? 1 : (parts > 64 ? 64 : parts);
+    const dim3 grid(tokens, parts);
+    if (is_bf16) rotate_heads_kernel<<<grid, ROTATE_THREADS, 0, stream>>>((__nv_bfloat16*)x, stride, col0, heads, head_dim, rot_dims, rot_half, inv_freq, positions, sign);
+    else rotate_heads_kernel<<<grid, ROTATE_THREADS, 0, stream>>>((float*)x, stride, col0, heads, head_dim, rot_dims, rot_half, inv_freq, positions, sign);
+    return launch_status();
+}

@@ -11,6 +11,14 @@
 //   gather:   xs[slot] = weight * x[token] (the weight multiplies what the expert reads); padding rows are left as they are
 //   product:  C[slot] = A[slot] W[expert of slot's tile]^T, float accumulation in one chain over k per output
 //   combine:  out[token] = base[token] + sum over choices of y[slot_of[token, choice]], in the order of the choices
+//
+// A second router and a second combine serve feed-forwards whose router scores are a softmax, whose choice is made on score + a
+// correction inside the best groups of neighbouring experts, whose last router outputs are experts without matrices that hand
+// their input on as it is, and whose weights multiply what an expert returns:
+//   route_scored:      s = softmax(z) over all outputs; c = s + correction; only outputs of the `keep` groups with the largest
+//                      best c can be chosen; the `top` largest c; weight = s * scale
+//   plan:              a choice >= experts takes no slot (slot_of = -1); without weights every slot's weight is 1
+//   combine_weighted:  out[token] = sigmoid(gate[token]) * base[token] + sum over choices of w * (y[slot] or, without a slot, x[token])
 #include "common.cuh"
 
 namespace {
@@ -20,13 +28,9 @@ constexpr int ROUTE_THREADS = 256;
 // columns in four chains of its own (columns beyond a multiple of four go to the first chain), the chains are added in a fixed
 // order and the lanes meet in a butterfly: a logit depends on nothing but the row and the expert's weights.
 template <typename T>
-__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ router, int hidden,
-                                                                  int experts, int top, int weighted, int* __restrict__ chosen,
-                                                                  float* __restrict__ weights) {
-    extern __shared__ __align__(16) float shared[];  // the token's row (padded to a multiple of four), then one logit per expert
-    float* row = shared;
+__device__ __forceinline__ void router_logits(const T* __restrict__ x, int x_stride, const float* __restrict__ router, int hidden, int experts, float* row,
+                                              float* logit) {
     const int padded = (hidden + 3) & ~3;
-    float* logit = shared + padded;
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < padded; i += ROUTE_THREADS) row[i] = i < hidden ? to_float(x[(size_t)t * x_stride + i]) : 0.f;
     __syncthreads();
@@ -51,6 +55,17 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __res
         if (lane == 0) logit[e] = sum;
     }
     __syncthreads();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ router, int hidden,
+                                                                  int experts, int top, int weighted, int* __restrict__ chosen,
+                                                                  float* __restrict__ weights) {
+    extern __shared__ __align__(16) float shared[];  // the token's row (padded to a multiple of four), then one logit per expert
+    float* row = shared;
+    float* logit = shared + ((hidden + 3) & ~3);
+    const int t = blockIdx.x;
+    router_logits(x, x_stride, router, hidden, experts, row, logit);
     if (threadIdx.x == 0) {
         for (int k = 0; k < top; ++k) {
             int best = -1;
@@ -62,6 +77,89 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __res
             weights[(size_t)t * top + k] = weighted ? 1.0f / (1.0f + expf(-value)) : 1.f;
             logit[best] = -INFINITY;
         }
+    }
+}
+
+// The largest value among the lanes, the lowest index among equals; a lane without a candidate brings index INT_MAX.
+__device__ __forceinline__ void warp_best(float& value, int& index) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, value, offset);
+        const int where = __shfl_xor_sync(0xffffffffu, index, offset);
+        if (where != 0x7fffffff && (index == 0x7fffffff || other > value || (other == value && where < index))) { value = other; index = where; }
+    }
+}
+
+// Softmax scores over all `outputs` of the router, choice by score + correction inside the best `group_keep` of `group_count` groups of
+// neighbours (a group's rank is its largest choice score; group_count <= 1: no groups), weights = plain score * scale.  The logits are
+// taken as in the kernel above; everything after them is the first warp's work, sums and searches in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_scored_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ router,
+                                                                         const float* __restrict__ correction, int hidden, int outputs, int top,
+                                                                         int group_count, int group_keep, float scale, int* __restrict__ chosen,
+                                                                         float* __restrict__ weights) {
+    extern __shared__ __align__(16) float shared[];  // the row, then per output: logit, score, choice score, a flag; then per group: best, a flag
+    float* row = shared;
+    float* logit = shared + ((hidden + 3) & ~3);
+    float* score = logit + outputs;
+    float* choice = score + outputs;
+    int* dead = reinterpret_cast<int*>(choice + outputs);
+    float* group_best = reinterpret_cast<float*>(dead + outputs);
+    int* group_kept = reinterpret_cast<int*>(group_best + (group_count > 0 ? group_count : 1));
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    router_logits(x, x_stride, router, hidden, outputs, row, logit);
+    if (threadIdx.x >= 32) return;
+    float most = -INFINITY;
+    for (int e = lane; e < outputs; e += 32) most = fmaxf(most, logit[e]);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) most = fmaxf(most, __shfl_xor_sync(0xffffffffu, most, offset));
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) {
+        const float p = expf(logit[e] - most);
+        score[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < outputs; e += 32) {
+        score[e] = score[e] / sum;
+        choice[e] = score[e] + (correction ? correction[e] : 0.f);
+        dead[e] = 0;
+    }
+    __syncwarp();
+    if (group_count > 1 && group_keep < group_count) {
+        const int per = outputs / group_count;
+        for (int g = lane; g < group_count; g += 32) {
+            float best = -INFINITY;
+            for (int i = 0; i < per; ++i) best = fmaxf(best, choice[g * per + i]);
+            group_best[g] = best;
+            group_kept[g] = 0;
+        }
+        __syncwarp();
+        for (int k = 0; k < group_keep; ++k) {
+            float value = -INFINITY;
+            int index = 0x7fffffff;
+            for (int g = lane; g < group_count; g += 32)
+                if (!group_kept[g] && (index == 0x7fffffff || group_best[g] > value)) { value = group_best[g]; index = g; }
+            warp_best(value, index);
+            if (lane == 0 && index != 0x7fffffff) group_kept[index] = 1;
+            __syncwarp();
+        }
+        for (int e = lane; e < outputs; e += 32) dead[e] = !group_kept[e / per];
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float value = -INFINITY;
+        int index = 0x7fffffff;
+        for (int e = lane; e < outputs; e += 32)
+            if (!dead[e] && (index == 0x7fffffff || choice[e] > value)) { value = choice[e]; index = e; }
+        warp_best(value, index);
+        if (index == 0x7fffffff) index = 0;  // only when fewer outputs can be chosen than are asked for
+        if (lane == 0) {
+            chosen[(size_t)t * top + k] = index;
+            weights[(size_t)t * top + k] = score[index] * scale;
+            dead[index] = 1;
+        }
+        __syncwarp();
     }
 }
 
@@ -78,7 +176,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int* __res
     for (int s = tid; s < capacity; s += PLAN_THREADS) { slot_token[s] = -1; slot_weight[s] = 0.f; }
     for (int i = tid; i < capacity / pad; i += PLAN_THREADS) { tile_expert[i] = -1; tile_rows[i] = 0; }
     __syncthreads();
-    for (int i = tid; i < pairs; i += PLAN_THREADS) atomicAdd(&count[chosen[i]], 1);
+    for (int i = tid; i < pairs; i += PLAN_THREADS)
+        if (chosen[i] < experts) atomicAdd(&count[chosen[i]], 1);  // a choice beyond the experts with matrices takes no row
     __syncthreads();
     if (tid == 0) {
         int at = 0;
@@ -97,10 +196,11 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int* __res
     // which slot of its expert's run a pair takes depends on the order of the atomics; a row's result does not depend on its slot
     for (int i = tid; i < pairs; i += PLAN_THREADS) {
         const int e = chosen[i];
+        if (e >= experts) { slot_of[i] = -1; continue; }
         const int slot = start[e] + atomicAdd(&count[e], 1);
         slot_of[i] = slot;
         slot_token[slot] = i / top;
-        slot_weight[slot] = weights[i];
+        slot_weight[slot] = weights ? weights[i] : 1.f;
     }
 }
 
@@ -223,7 +323,61 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
         out[(size_t)t * hidden + i] = from_float<TO>(sum);
     }
 }
+
+// out[t] = sigmoid(base_gate[t]) * base[t] + sum_k w[t, k] * (slot_of[t, k] >= 0 ? y[slot] : x[t]), added in the order of the choices, in float.
+template <typename T>
+__global__ void moe_combine_weighted_kernel(const T* __restrict__ y, const int* __restrict__ slot_of, const float* __restrict__ weights, int top,
+                                            const T* __restrict__ x, int x_stride, const T* __restrict__ base, const float* __restrict__ base_gate,
+                                            T* __restrict__ out, int hidden) {
+    const int t = blockIdx.x;
+    const float share = base ? (base_gate ? 1.0f / (1.0f + expf(-base_gate[t])) : 1.f) : 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float sum = base ? share * to_float(base[(size_t)t * hidden + i]) : 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int slot = slot_of[(size_t)t * top + k];
+            const float v = slot >= 0 ? to_float(y[(size_t)slot * hidden + i]) : to_float(x[(size_t)t * x_stride + i]);
+            sum = fmaf(weights[(size_t)t * top + k], v, sum);
+        }
+        out[(size_t)t * hidden + i] = from_float<T>(sum);
+    }
+}
 }  // namespace
+
+HB_EXPORT int hb_moe_route_scored(const void* x, int is_bf16, int x_stride, const float* router, const float* correction, int tokens, int hidden,
+                                  int outputs, int top, int group_count, int group_keep, float scale, int* chosen, float* weights, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (outputs <= 0 || outputs > 1024 || top <= 0 || top > outputs || hidden <= 0) return HB_UNSUPPORTED_SIZE;
+    if (group_count > 1 && (outputs % group_count || group_keep <= 0 || group_keep > group_count || top > group_keep * (outputs / group_count)))
+        return HB_BAD_ARGUMENT;
+    const size_t shared = (size_t)(((hidden + 3) & ~3) + 4 * outputs + 2 * (group_count > 0 ? group_count : 1)) * sizeof(float);
+    if (shared > 200 * 1024) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(moe_route_scored_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        moe_route_scored_kernel<<<tokens, ROUTE_THREADS, shared, stream>>>((const __nv_bfloat16*)x, x_stride, router, correction, hidden, outputs, top,
+                                                                          group_count, group_keep, scale, chosen, weights);
+    } else {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(moe_route_scored_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        moe_route_scored_kernel<<<tokens, ROUTE_THREADS, shared, stream>>>((const float*)x, x_stride, router, correction, hidden, outputs, top, group_count,
+                                                                          group_keep, scale, chosen, weights);
+    }
+    return launch_status();
+}
+
+// y [capacity, hidden], x [tokens, x_stride] (what the feed-forward read), base [tokens, hidden] (optional, with an optional gate per token)
+// and out [tokens, hidden] share an element type; weights [tokens, top] float.
+HB_EXPORT int hb_moe_combine_weighted(const void* y, const int* slot_of, const float* weights, int top, const void* x, int x_stride, const void* base,
+                                      const float* base_gate, void* out, int is_bf16, int tokens, int hidden, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (!weights || !x || top <= 0) return HB_BAD_ARGUMENT;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16)
+        moe_combine_weighted_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)y, slot_of, weights, top, (const __nv_bfloat16*)x, x_stride,
+                                                                    (const __nv_bfloat16*)base, base_gate, (__nv_bfloat16*)out, hidden);
+    else
+        moe_combine_weighted_kernel<<<tokens, threads, 0, stream>>>((const float*)y, slot_of, weights, top, (const float*)x, x_stride, (const float*)base,
+                                                                    base_gate, (float*)out, hidden);
+    return launch_status();
+}
 
 HB_EXPORT int hb_moe_route(const void* x, int is_bf16, int x_stride, const float* router, int tokens, int hidden, int experts, int top, int weighted,
                            int* chosen, float* weights, cudaStream_t stream) {

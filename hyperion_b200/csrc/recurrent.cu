@@ -12,6 +12,8 @@
 //     retention:    S <- a S + k v^T  (a fixed per head);           o = S^T q
 //     wkv:          o = S^T q + (sum_i u_i k_i q_i) v;  S <- diag(w) S + k v^T,  w_i = exp(-exp(x_i + w0_i))
 //                   (a decay per key entry computed from the token, and a bonus u that only the current token gets)
+//     channel delta: S <- diag(g) S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q,  g_i = exp(-exp(A_log) softplus(x_i + bias_i))
+//                   (the delta rule with a decay per key entry computed from the token)
 // Column j of S (one value dimension) never meets another column, so the work is cut by columns:
 // eight lanes share a column, each holding n / 8 of its entries in registers (groups of four
 // consecutive entries, stored as S^T so that they are one 16-byte access), and a block of 128
@@ -23,7 +25,7 @@
 
 namespace {
 constexpr int SCAN_THREADS = 128;
-enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1, MODE_RETENTION = 2, MODE_WKV = 3 };
+enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1, MODE_RETENTION = 2, MODE_WKV = 3, MODE_CHANNEL_DELTA = 4 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -71,6 +73,8 @@ struct ScanArgs {
     int k_stride, q_stride, v_stride;
     const float* proj;   // [tokens, proj_stride]: raw projections that give the decay and the step (wkv: heads * n entries at decay_off)
     int proj_stride, decay_off, step_off;
+    const float* step;   // [tokens, step_stride]: the raw projection that gives the delta rule's step, head h at step_off + h (the modes whose step lies beside the decay: proj itself)
+    int step_stride;
     const float* a_log;  // [heads] (wkv: w0 [heads * n])
     const float* dt_bias;  // [heads] (wkv: the bonus u [heads * n])
     const float* skip;   // [heads] (state space: D)
@@ -93,11 +97,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     // from shared memory once for all of them, and the columns' chains, which never meet, fill one another's waits (a prompt
     // gives the GPU fewer warps than it has schedulers, so nothing else would).
     constexpr int NP = NG * 4 * LPC, NPR = NP / 32, GROUPS = 128 / LPC, COLUMNS = GROUPS * CPT, VR = (COLUMNS + 31) / 32;
-    constexpr bool WKV = MODE == MODE_WKV;  // a third vector per token (its decays) passes through shared memory: shorter chunks
-    constexpr int CT = WKV ? (NP >= 256 ? 4 : (NP >= 128 ? 8 : 16)) : (NP >= 256 ? 8 : 16), PER_WARP = CT / 4;
+    constexpr bool WKV = MODE == MODE_WKV, CHANNEL = MODE == MODE_CHANNEL_DELTA, DELTA = MODE == MODE_DELTA || CHANNEL;
+    constexpr bool VEC = WKV || CHANNEL;  // a third vector per token (its decays) passes through shared memory: shorter chunks
+    constexpr int CT = VEC ? (NP >= 256 ? 4 : (NP >= 128 ? 8 : 16)) : (NP >= 256 ? 8 : 16), PER_WARP = CT / 4;
     __shared__ __align__(16) float sk[2][CT][NP];
     __shared__ __align__(16) float sq[2][CT][NP];
-    __shared__ __align__(16) float sw[WKV ? 2 : 1][WKV ? CT : 1][WKV ? NP : 4];
+    __shared__ __align__(16) float sw[VEC ? 2 : 1][VEC ? CT : 1][VEC ? NP : 4];
     __shared__ float sv[2][CT][VR * 32], sdecay[2][CT], sstep[2][CT];
 
     const int row = blockIdx.z, head = blockIdx.y;
@@ -122,17 +127,17 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     }
     const float a_rate = (MODE == MODE_RETENTION || WKV) ? 0.f : expf(a.a_log[head]);
     const float fixed_decay = MODE == MODE_RETENTION ? a.a_log[head] : 0.f;
-    const float bias = (MODE == MODE_RETENTION || WKV) ? 0.f : a.dt_bias[head];
-    float w0[NPR], bonus[NPR];  // wkv: this lane's entries of the head's decay offset and bonus
+    const float bias = (MODE == MODE_RETENTION || VEC) ? 0.f : a.dt_bias[head];
+    float w0[NPR], bonus[NPR];  // wkv: this lane's entries of the head's decay offset and bonus; channel delta: of the decay's bias
 #pragma unroll
     for (int r = 0; r < NPR; ++r) {
         const int index = lane + 32 * r;
-        w0[r] = (WKV && index < a.n) ? a.a_log[(size_t)head * a.n + index] : 0.f;
+        w0[r] = (VEC && index < a.n) ? (WKV ? a.a_log : a.dt_bias)[(size_t)head * a.n + index] : 0.f;
         bonus[r] = (WKV && index < a.n) ? a.dt_bias[(size_t)head * a.n + index] : 0.f;
     }
     const float skip = MODE == MODE_STATE_SPACE ? a.skip[head] : 0.f;
 
-    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP][VR], pdecay[PER_WARP], pstep[PER_WARP], pw[PER_WARP][WKV ? NPR : 1];
+    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP][VR], pdecay[PER_WARP], pstep[PER_WARP], pw[PER_WARP][VEC ? NPR : 1];
     auto prefetch = [&](int first) {
 #pragma unroll
         for (int i = 0; i < PER_WARP; ++i) {
@@ -154,15 +159,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 pv[i][r] = (live && column < COLUMNS && col0 + column < a.e) ? vals[col0 + column] : 0.f;
             }
             const float* p = a.proj + at * a.proj_stride;
-            if (WKV) {
+            if (VEC) {
 #pragma unroll
                 for (int r = 0; r < NPR; ++r) {
                     const int index = lane + 32 * r;
                     pw[i][r] = (live && index < a.n) ? p[a.decay_off + (size_t)head * a.n + index] : 0.f;
                 }
             }
-            pdecay[i] = (live && MODE != MODE_RETENTION && !WKV) ? p[a.decay_off + head] : 0.f;
-            pstep[i] = (live && MODE == MODE_DELTA) ? p[a.step_off + head] : 0.f;
+            pdecay[i] = (live && MODE != MODE_RETENTION && !VEC) ? p[a.decay_off + head] : 0.f;
+            pstep[i] = (live && DELTA) ? a.step[at * a.step_stride + a.step_off + head] : 0.f;
         }
     };
     auto publish = [&](int buffer) {
@@ -170,7 +175,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
         for (int i = 0; i < PER_WARP; ++i) {
             const int j = warp + 4 * i;
             float ik = 1.f, iq = 1.f;
-            if (MODE == MODE_DELTA) {  // keys and queries become unit vectors; the query also takes the scale
+            if (DELTA) {  // keys and queries become unit vectors; the query also takes the scale
                 float sum_k = 0.f, sum_q = 0.f;
 #pragma unroll
                 for (int r = 0; r < NPR; ++r) { sum_k = fmaf(pk[i][r], pk[i][r], sum_k); sum_q = fmaf(pq[i][r], pq[i][r], sum_q); }
@@ -193,11 +198,18 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 }
                 bonus_dot = warp_sum(bonus_dot);
             }
+            if (CHANNEL) {  // the entries' decays
+#pragma unroll
+                for (int r = 0; r < NPR; ++r) sw[buffer][j][lane + 32 * r] = expf(-a_rate * softplus_f(pw[i][r] + w0[r]));
+            }
             if (lane == 0) {
                 float decay, step;
                 if (WKV) {
                     decay = 1.f;
                     step = bonus_dot;
+                } else if (CHANNEL) {
+                    decay = 1.f;
+                    step = 1.0f / (1.0f + expf(-pstep[i]));
                 } else if (MODE == MODE_DELTA) {
                     decay = expf(-a_rate * softplus_f(pdecay[i] + bias));
                     step = 1.0f / (1.0f + expf(-pstep[i]));
@@ -235,13 +247,15 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
             float cv[CPT], u[CPT], o[CPT];
 #pragma unroll
             for (int c = 0; c < CPT; ++c) cv[c] = sv[buffer][j][cw + GROUPS * c];
-            if (WKV) {
-                float cd[NG][4];
+            float cd[VEC ? NG : 1][4];
+            if (VEC) {
 #pragma unroll
                 for (int r = 0; r < NG; ++r) {
                     const float4 d4 = *reinterpret_cast<const float4*>(&sw[buffer][j][4 * (LPC * r + l)]);
                     cd[r][0] = d4.x; cd[r][1] = d4.y; cd[r][2] = d4.z; cd[r][3] = d4.w;
                 }
+            }
+            if (WKV) {
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) {  // the query meets the state as the token found it; then the state fades and takes k v^T
                     float part[4] = {0.f, 0.f, 0.f, 0.f};
@@ -265,7 +279,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 }
                 continue;
             }
-            if (MODE == MODE_DELTA) {
+            if (DELTA) {
                 float dot[CPT];
 #pragma unroll
                 for (int c = 0; c < CPT; ++c) {
@@ -273,7 +287,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
 #pragma unroll
                     for (int r = 0; r < NG; ++r)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) { s[c][r][i] *= decay; part[i] = fmaf(s[c][r][i], ck[r][i], part[i]); }
+                        for (int i = 0; i < 4; ++i) { s[c][r][i] *= CHANNEL ? cd[CHANNEL ? r : 0][i] : decay; part[i] = fmaf(s[c][r][i], ck[r][i], part[i]); }
                     dot[c] = (part[0] + part[1]) + (part[2] + part[3]);
                 }
 #pragma unroll
@@ -338,7 +352,7 @@ int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
     // reduction to the chain, rose from 783 / 939 us to 960 with two and 1,071 with four; eight decoded tokens gain a fifth either way.
     constexpr int LANES = 8;
     const int per_lane = (a.n_padded + 4 * LANES - 1) / (4 * LANES);  // groups of four entries per lane
-    constexpr int PER_THREAD = MODE == MODE_DELTA ? 1 : 2;  // wkv: two, like the other recurrences whose columns add no reduction to the chain
+    constexpr int PER_THREAD = (MODE == MODE_DELTA || MODE == MODE_CHANNEL_DELTA) ? 1 : 2;  // wkv: two, like the other recurrences whose columns add no reduction to the chain
     const int columns = (128 / LANES) * PER_THREAD;
     const dim3 grid((a.e + columns - 1) / columns, a.heads, rows);
     if (per_lane <= 1) state_scan_kernel<1, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
@@ -350,12 +364,14 @@ int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
 
 // ---------------------------------------------------------------- gated group norm
 // One block per (token, group of `group` columns).  gate_first: v = y * silu(g), out = v / rms(v) * w; otherwise
-// out = y / rms(y) * w * silu(g).  The weight has `weight_len` entries and is indexed by column % weight_len (a weight
+// out = y / rms(y) * w * silu(g); with sigmoid_gate the gate is sigmoid(g) instead of silu(g).  The weight has `weight_len` entries and is indexed by column % weight_len (a weight
 // of one head's size is shared by all heads; no weight at all: a plain unit RMS).  `scale` multiplies the result before its one rounding.
+__device__ __forceinline__ float gate_f(float z, int sigmoid_gate) { return sigmoid_gate ? 1.0f / (1.0f + expf(-z)) : silu_f(z); }
+
 template <typename TO>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ gate, int gate_stride,
                                         int gate_off, const float* __restrict__ weight, int weight_len, int group, int gate_first,
-                                        float eps, float scale, TO* __restrict__ out, int out_stride) {
+                                        float eps, float scale, TO* __restrict__ out, int out_stride, int sigmoid_gate) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, first = blockIdx.y * group;
     const float* yrow = y + (size_t)t * y_stride + first;
@@ -363,12 +379,12 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_strid
     float sum = 0.f;
     for (int j = threadIdx.x; j < group; j += blockDim.x) {
         float v = yrow[j];
-        if (gate_first) v *= silu_f(grow[j]);
+        if (gate_first) v *= gate_f(grow[j], sigmoid_gate);
         sum = fmaf(v, v, sum);
     }
     const float inv = 1.0f / sqrtf(block_sum(sum, scratch) / (float)group + eps);
     for (int j = threadIdx.x; j < group; j += blockDim.x) {
-        const float g = silu_f(grow[j]);
+        const float g = gate_f(grow[j], sigmoid_gate);
         float v = yrow[j];
         if (gate_first) v *= g;
         v = v * inv * (weight ? weight[(first + j) % weight_len] : 1.f);
@@ -382,7 +398,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_strid
 template <typename TO>
 __global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ gate, int gate_stride,
                                              int gate_off, const float* __restrict__ weight, int weight_len, int group, int groups, int gate_first,
-                                             float eps, float scale, TO* __restrict__ out, int out_stride) {
+                                             float eps, float scale, TO* __restrict__ out, int out_stride, int sigmoid_gate) {
     const int t = blockIdx.x, which = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (which >= groups) return;
     const int first = which * group;
@@ -391,12 +407,12 @@ __global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, int y_
     float sum = 0.f;
     for (int j = lane; j < group; j += 32) {
         float v = yrow[j];
-        if (gate_first) v *= silu_f(grow[j]);
+        if (gate_first) v *= gate_f(grow[j], sigmoid_gate);
         sum = fmaf(v, v, sum);
     }
     const float inv = 1.0f / sqrtf(warp_sum(sum) / (float)group + eps);
     for (int j = lane; j < group; j += 32) {
-        const float g = silu_f(grow[j]);
+        const float g = gate_f(grow[j], sigmoid_gate);
         float v = yrow[j];
         if (gate_first) v *= g;
         v = v * inv * (weight ? weight[(first + j) % weight_len] : 1.f);
@@ -439,12 +455,27 @@ HB_EXPORT int hb_state_scan(int mode, const float* conv, int conv_stride, int k_
     if (rows <= 0) return 0;
     if (n <= 0 || n > 256 || e <= 0 || heads <= 0 || groups <= 0 || heads % groups || rows > 65535 || heads > 65535) return HB_UNSUPPORTED_SIZE;
     if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15)) return HB_BAD_ARGUMENT;
-    ScanArgs a{conv + k_off, conv + q_off, conv + v_off, conv_stride, conv_stride, conv_stride, proj, proj_stride, decay_off, step_off, a_log, dt_bias, skip,
+    ScanArgs a{conv + k_off, conv + q_off, conv + v_off, conv_stride, conv_stride, conv_stride, proj, proj_stride, decay_off, step_off, proj, proj_stride, a_log, dt_bias, skip,
                state, (size_t)slot_stride, state_off, slots, row_start, out, heads, groups, n, n_padded, e, q_scale};
     if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, rows, stream);
     if (mode == MODE_STATE_SPACE) return launch_scan<MODE_STATE_SPACE>(a, rows, stream);
     if (mode == MODE_RETENTION) return launch_scan<MODE_RETENTION>(a, rows, stream);
     return HB_BAD_ARGUMENT;
+}
+
+// The delta rule with a decay per key entry (see the head of this file): keys, queries and values at k_off, q_off and v_off of `conv`
+// (groups * n, groups * n and heads * e columns), the decays' pre-activations in `decay` [tokens, heads * n] with their bias
+// dt_bias [heads * n] and the rate a_log [heads], the step's pre-activation (one per head) at step_off of `step`.  The state as in hb_state_scan.
+HB_EXPORT int hb_channel_delta_scan(const float* conv, int conv_stride, int k_off, int q_off, int v_off, const float* decay, int decay_stride, int decay_off,
+                                    const float* step, int step_stride, int step_off, const float* a_log, const float* dt_bias, float* state,
+                                    long long slot_stride, int state_off, const int* slots, const int* row_start, float* out, int rows, int heads,
+                                    int groups, int n, int n_padded, int e, float q_scale, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0 || n > 256 || e <= 0 || heads <= 0 || groups <= 0 || heads % groups || rows > 65535 || heads > 65535) return HB_UNSUPPORTED_SIZE;
+    if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15) || !a_log || !dt_bias) return HB_BAD_ARGUMENT;
+    ScanArgs a{conv + k_off, conv + q_off, conv + v_off, conv_stride, conv_stride, conv_stride, decay, decay_stride, decay_off, step_off, step, step_stride,
+               a_log, dt_bias, nullptr, state, (size_t)slot_stride, state_off, slots, row_start, out, heads, groups, n, n_padded, e, q_scale};
+    return launch_scan<MODE_CHANNEL_DELTA>(a, rows, stream);
 }
 
 // The wkv recurrence: keys, queries and values from three float matrices of their own (heads * n, heads * n and heads * e columns), the
@@ -455,7 +486,7 @@ HB_EXPORT int hb_wkv_scan(const float* k, int k_stride, const float* q, int q_st
     if (rows <= 0) return 0;
     if (n <= 0 || n > 256 || e <= 0 || heads <= 0 || rows > 65535 || heads > 65535) return HB_UNSUPPORTED_SIZE;
     if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15) || !w0 || !bonus) return HB_BAD_ARGUMENT;
-    ScanArgs a{k, q, v, k_stride, q_stride, v_stride, x, x_stride, x_off, 0, w0, bonus, nullptr, state, (size_t)slot_stride, state_off, slots, row_start, out,
+    ScanArgs a{k, q, v, k_stride, q_stride, v_stride, x, x_stride, x_off, 0, x, x_stride, w0, bonus, nullptr, state, (size_t)slot_stride, state_off, slots, row_start, out,
                heads, heads, n, n_padded, e, 1.f};
     return launch_scan<MODE_WKV>(a, rows, stream);
 }
@@ -573,7 +604,7 @@ HB_EXPORT int hb_tanh_rows(const float* x, void* out, int out_is_bf16, long long
 
 HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gate, int gate_stride, int gate_off, const float* weight,
                                   int weight_len, int group, int groups, int gate_first, float eps, float scale, void* out, int out_is_bf16,
-                                  int out_stride, int tokens, cudaStream_t stream) {
+                                  int out_stride, int tokens, int sigmoid_gate, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (group <= 0 || groups <= 0 || groups > 65535 || (weight && weight_len <= 0)) return HB_UNSUPPORTED_SIZE;
     if (!weight) weight_len = 1;
@@ -581,20 +612,100 @@ HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gat
         const dim3 warps(tokens, (groups + 3) / 4);
         if (out_is_bf16)
             gated_group_norm_warp_kernel<<<warps, 128, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, groups, gate_first,
-                                                                    eps, scale, (__nv_bfloat16*)out, out_stride);
+                                                                    eps, scale, (__nv_bfloat16*)out, out_stride, sigmoid_gate);
         else
             gated_group_norm_warp_kernel<<<warps, 128, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, groups, gate_first,
-                                                                    eps, scale, (float*)out, out_stride);
+                                                                    eps, scale, (float*)out, out_stride, sigmoid_gate);
         return launch_status();
     }
     const int threads = 256;
     const dim3 grid(tokens, groups);
     if (out_is_bf16)
         gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps, scale,
-                                                              (__nv_bfloat16*)out, out_stride);
+                                                              (__nv_bfloat16*)out, out_stride, sigmoid_gate);
     else
         gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps, scale,
-                                                              (float*)out, out_stride);
+                                                              (float*)out, out_stride, sigmoid_gate);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- a convolution added to its own input
+// out[t, c] = x[t, c] + sum_j weight[c, j] * x[t - (taps - 1 - j), c] over the tokens of t's own request (the last column of the weight
+// multiplies the current token); inputs before the row's first token come from the request's state (its last taps - 1 inputs as floats,
+// oldest first; zero for a new request).  Rows and result share an element type; the sum is float, rounded once.
+// hb_conv_state_keep then stores every row's last taps - 1 inputs for the next step.  silu_columns: silu in place over some columns of float rows.
+namespace {
+template <typename T>
+__global__ void residual_conv_kernel(const T* __restrict__ x, int x_stride, int channels, const float* __restrict__ weight, int taps,
+                                     const float* __restrict__ state, size_t slot_stride, int state_off, const int* __restrict__ slots,
+                                     const int* __restrict__ token_row, const int* __restrict__ row_start, T* __restrict__ out, int out_stride, int first_token) {
+    const int t = first_token + blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int r = token_row[t];
+    const int i = t - row_start[r];
+    const float* kept = state + (size_t)slots[r] * slot_stride + state_off;
+    float acc = 0.f;
+    for (int j = taps - 1; j >= 0; --j) {  // oldest input first
+        const float w = weight[(size_t)c * taps + taps - 1 - j];
+        const float v = (i - j >= 0) ? to_float(x[(size_t)(t - j) * x_stride + c]) : kept[(size_t)(taps - 1 + i - j) * channels + c];
+        acc = fmaf(w, v, acc);
+    }
+    out[(size_t)t * out_stride + c] = from_float<T>(to_float(x[(size_t)t * x_stride + c]) + acc);
+}
+
+template <typename T>
+__global__ void conv_state_keep_kernel(const T* __restrict__ x, int x_stride, int channels, int taps, float* __restrict__ state, size_t slot_stride,
+                                       int state_off, const int* __restrict__ slots, const int* __restrict__ row_start, int rows) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= channels || r >= rows) return;
+    const int first = row_start[r], n = row_start[r + 1] - first, keep = taps - 1;
+    float* kept = state + (size_t)slots[r] * slot_stride + state_off;
+    for (int s = 0; s < keep; ++s) {  // ascending: an old entry is read (at s + n > s) before it is overwritten
+        const int src = n - keep + s;
+        kept[(size_t)s * channels + c] = src >= 0 ? to_float(x[(size_t)(first + src) * x_stride + c]) : kept[(size_t)(s + n) * channels + c];
+    }
+}
+
+__global__ void silu_columns_kernel(float* __restrict__ x, int x_stride, int col0, int columns, long long count) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        float* p = x + (size_t)(i / columns) * x_stride + col0 + (int)(i % columns);
+        *p = silu_f(*p);
+    }
+}
+}  // namespace
+
+HB_EXPORT int hb_residual_conv(const void* x, int is_bf16, int x_stride, int channels, const float* weight, int taps, const float* state,
+                               long long slot_stride, int state_off, const int* slots, const int* token_row, const int* row_start, void* out,
+                               int out_stride, int tokens, cudaStream_t stream) {
+    if (tokens <= 0 || channels <= 0) return 0;
+    if (taps < 1) return HB_BAD_ARGUMENT;
+    for (int first = 0; first < tokens; first += 65535) {
+        const int count = tokens - first < 65535 ? tokens - first : 65535;
+        const dim3 grid((channels + 255) / 256, count);
+        if (is_bf16)
+            residual_conv_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, weight, taps, state, (size_t)slot_stride, state_off, slots,
+                                                           token_row, row_start, (__nv_bfloat16*)out, out_stride, first);
+        else
+            residual_conv_kernel<<<grid, 256, 0, stream>>>((const float*)x, x_stride, channels, weight, taps, state, (size_t)slot_stride, state_off, slots,
+                                                           token_row, row_start, (float*)out, out_stride, first);
+    }
+    return launch_status();
+}
+
+HB_EXPORT int hb_conv_state_keep(const void* x, int is_bf16, int x_stride, int channels, int taps, float* state, long long slot_stride, int state_off,
+                                 const int* slots, const int* row_start, int rows, cudaStream_t stream) {
+    if (rows <= 0 || channels <= 0 || taps <= 1) return 0;
+    if (rows > 65535) return HB_UNSUPPORTED_SIZE;
+    const dim3 grid((channels + 127) / 128, rows);
+    if (is_bf16) conv_state_keep_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, taps, state, (size_t)slot_stride, state_off, slots, row_start, rows);
+    else conv_state_keep_kernel<<<grid, 128, 0, stream>>>((const float*)x, x_stride, channels, taps, state, (size_t)slot_stride, state_off, slots, row_start, rows);
+    return launch_status();
+}
+
+HB_EXPORT int hb_silu_columns(float* x, int x_stride, int col0, int columns, int tokens, cudaStream_t stream) {
+    if (tokens <= 0 || columns <= 0) return 0;
+    const long long count = (long long)tokens * columns, wanted = (count + 255) / 256;
+    silu_columns_kernel<<<(int)(wanted < 4096 ? wanted : 4096), 256, 0, stream>>>(x, x_stride, col0, columns, count);
     return launch_status();
 }
 

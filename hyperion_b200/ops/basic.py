@@ -455,3 +455,36 @@ def sgemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None =
         check(lib.hb_sgemm_f32(ptr(x[start:]), ptr(weight), ptr(bias), ptr(out[start:]), i32(count), i32(n), i32(k),
                                i32(x.stride(0)), i32(out.stride(0)), stream_ptr()), "sgemm_f32")
     return out
+
+
+def gelu_erf(x: torch.Tensor) -> torch.Tensor:
+    """0.5 z (1 + erf(z / sqrt(2))), computed in float, in the element type of ``x``."""
+    require_cuda(x)
+    if not x.is_contiguous():
+        raise KernelError("gelu_erf: a dense tensor")
+    out = torch.empty_like(x)
+    check(library("elementwise").hb_gelu_erf(ptr(x), ptr(out), i32(is_bf16(x)), ctypes.c_longlong(x.numel()), stream_ptr()), "gelu_erf")
+    return out
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x <- x * scale in place over a dense float32 tensor."""
+    require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_: a dense float32 tensor")
+    check(library("elementwise").hb_scale_rows(ptr(x), f32(scale), ctypes.c_longlong(x.numel()), stream_ptr()), "scale_rows")
+    return x
+
+
+def rotate_heads_(x: torch.Tensor, col0: int, heads: int, head_dim: int, positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, rot_half: bool,
+                  sign: float = 1.0) -> None:
+    """Every head of the columns ``col0 .. col0 + heads * head_dim`` of ``x`` turns in place by ``sign`` times its token's position: within a
+    head's first ``rot_dims`` entries pair i (entry i with i + rot_dims / 2 when ``rot_half``, else 2i with 2i + 1) by the angle
+    sign * position * inv_freq[i].  Float arithmetic, one rounding at the store."""
+    require_cuda(x, positions, inv_freq)
+    if x.dim() != 2 or x.stride(1) != 1 or inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous() or inv_freq.numel() < rot_dims // 2:
+        raise KernelError("rotate_heads: rows with unit inner stride and a dense float32 frequency per pair")
+    if col0 < 0 or col0 + heads * head_dim > x.shape[1]:
+        raise KernelError("rotate_heads: the heads lie outside the rows")
+    check(library("heads_prepare").hb_rotate_heads(ptr(x), i32(is_bf16(x)), i32(x.shape[0]), i32(x.stride(0)), i32(col0), i32(heads), i32(head_dim), i32(rot_dims),
+                                                   i32(1 if rot_half else 0), ptr(inv_freq), ptr(positions), f32(sign), stream_ptr()), "rotate_heads")

@@ -9,7 +9,7 @@ from dataclasses import dataclass
 import torch
 
 from .basic import status_word
-from .native import KernelError, check, i32, is_bf16, library, ptr, require_cuda, stream_ptr
+from .native import KernelError, check, f32, i32, is_bf16, library, ptr, require_cuda, stream_ptr
 
 PAD = 128  # an expert's rows are padded to whole tiles of this many rows
 FEW_PAIRS = 128  # steps of at most this many (token, choice) pairs stream the matrices of the experts they use instead of taking tensor-core tiles
@@ -44,12 +44,34 @@ def route(x: torch.Tensor, router: torch.Tensor, top: int, weighted: bool = True
     return chosen, weights
 
 
+def route_scored(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, top: int, group_count: int, group_keep: int,
+                 scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """Router logits ``x router^T`` in float, scores = softmax over all outputs, choice scores = scores + ``correction``; only outputs of
+    the ``group_keep`` groups (of ``group_count`` equal groups of neighbours; at most 1: no groups) whose largest choice score is
+    largest can be chosen; the ``top`` largest choice scores (lowest index first among equals); weights = the plain scores of the
+    chosen times ``scale``, not renormalised: ([tokens, top] int32, [tokens, top] float)."""
+    require_cuda(x, router, correction)
+    if router.dtype != torch.float32 or not router.is_contiguous() or x.stride(-1) != 1 or x.shape[1] != router.shape[1]:
+        raise KernelError("moe.route_scored: a dense float32 router matrix [outputs, hidden] and rows with unit inner stride")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != router.shape[0] or not correction.is_contiguous()):
+        raise KernelError("moe.route_scored: the correction is a dense float32 vector with one entry per router output")
+    tokens, hidden = x.shape
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
+    check(library("moe").hb_moe_route_scored(ptr(x), i32(is_bf16(x)), i32(x.stride(0)), ptr(router), ptr(correction), i32(tokens), i32(hidden),
+                                             i32(router.shape[0]), i32(top), i32(group_count), i32(group_keep), f32(scale), ptr(chosen), ptr(weights),
+                                             stream_ptr()), "moe_route_scored")
+    return chosen, weights
+
+
 def capacity_for(pairs: int, experts: int, pad: int = PAD) -> int:
     """Rows the sorted buffers need whatever the routing: all pairs, each expert's run padded to whole tiles."""
     return -(-(pairs + experts * (pad - 1)) // pad) * pad
 
 
-def plan(chosen: torch.Tensor, weights: torch.Tensor, experts: int) -> Plan:
+def plan(chosen: torch.Tensor, weights: torch.Tensor | None, experts: int) -> Plan:
+    """``weights`` None: every row's weight is 1 (the weights then multiply what the experts return: :func:`combine_weighted`).  A choice
+    of ``experts`` or above (a router output without matrices) takes no row; its ``slot_of`` is -1."""
     require_cuda(chosen, weights)
     tokens, top = chosen.shape
     pairs = tokens * top
@@ -109,4 +131,23 @@ def combine(y: torch.Tensor, where: Plan, base: torch.Tensor | None, tokens: int
     out = torch.empty((tokens, y.shape[1]), dtype=y.dtype, device=y.device)
     check(library("moe").hb_moe_combine(ptr(y), ptr(where.slot_of), i32(where.top), ptr(base), ptr(out), i32(is_bf16(y)), i32(tokens), i32(y.shape[1]),
                                         stream_ptr()), "moe_combine")
+    return out
+
+
+def combine_weighted(y: torch.Tensor, where: Plan, weights: torch.Tensor, x: torch.Tensor, base: torch.Tensor | None, base_gate: torch.Tensor | None) -> torch.Tensor:
+    """out[t] = sigmoid(base_gate[t]) * base[t] + sum over t's choices of weight * (the choice's row of ``y``, or ``x[t]`` itself where the
+    choice took no row), added in the order of the choices, in float; rounded once.  ``base_gate`` [tokens] float (None: the base is
+    added as it is)."""
+    require_cuda(y, weights, x, base, base_gate)
+    tokens, hidden = x.shape
+    if (not y.is_contiguous() or y.shape[1] != hidden or x.dtype != y.dtype or x.stride(1) != 1 or weights.dtype != torch.float32 or not weights.is_contiguous()
+            or weights.shape != (tokens, where.top)):
+        raise KernelError("moe.combine_weighted: dense rows of one element type and float32 weights [tokens, top]")
+    if base is not None and (base.dtype != y.dtype or not base.is_contiguous() or base.shape != (tokens, hidden)):
+        raise KernelError("moe.combine_weighted: a base of the same element type and width")
+    if base_gate is not None and (base_gate.dtype != torch.float32 or base_gate.numel() != tokens or not base_gate.is_contiguous()):
+        raise KernelError("moe.combine_weighted: the base's gate is a dense float32 vector with one entry per token")
+    out = torch.empty((tokens, hidden), dtype=y.dtype, device=y.device)
+    check(library("moe").hb_moe_combine_weighted(ptr(y), ptr(where.slot_of), ptr(weights), i32(where.top), ptr(x), i32(x.stride(0)), ptr(base), ptr(base_gate),
+                                                 ptr(out), i32(is_bf16(y)), i32(tokens), i32(hidden), stream_ptr()), "moe_combine_weighted")
     return out

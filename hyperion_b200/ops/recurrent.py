@@ -43,6 +43,41 @@ def conv_state_update(x: torch.Tensor, col0: int, channels: int, taps: int, stat
                                                     stream_ptr()), "conv_state_update")
 
 
+def residual_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, state_off: int, slots: torch.Tensor, token_row: torch.Tensor,
+                  row_start: torch.Tensor) -> torch.Tensor:
+    """``x + conv(x)``: a causal convolution over time per column of ``x`` [tokens, C] with ``weight`` [C, taps] (the last column
+    multiplies the current token), added to its own input; a row's earlier inputs come from its slot of ``state`` (floats).  The
+    result has ``x``'s element type; the sum is float."""
+    require_cuda(x, weight, state, slots, token_row, row_start)
+    _floats(weight, state)
+    if x.dim() != 2 or x.stride(1) != 1 or weight.shape[0] != x.shape[1] or not weight.is_contiguous():
+        raise KernelError("residual_conv: rows with unit inner stride and a dense [columns, taps] weight")
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    check(library("recurrent").hb_residual_conv(ptr(x), i32(is_bf16(x)), i32(x.stride(0)), i32(x.shape[1]), ptr(weight), i32(weight.shape[1]), ptr(state),
+                                                ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(token_row), ptr(row_start), ptr(out),
+                                                i32(out.stride(0)), i32(x.shape[0]), stream_ptr()), "residual_conv")
+    return out
+
+
+def conv_state_keep(x: torch.Tensor, taps: int, state: torch.Tensor, state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int) -> None:
+    """Every row's slot keeps the last ``taps - 1`` rows of ``x`` (any element type, kept as floats) for the next step (call after
+    :func:`residual_conv` of the same step)."""
+    require_cuda(x, state, slots, row_start)
+    _floats(state)
+    check(library("recurrent").hb_conv_state_keep(ptr(x), i32(is_bf16(x)), i32(x.stride(0)), i32(x.shape[1]), i32(taps), ptr(state),
+                                                  ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start), i32(rows), stream_ptr()),
+          "conv_state_keep")
+
+
+def silu_columns_(x: torch.Tensor, col0: int, columns: int) -> None:
+    """silu in place over the columns ``col0 .. col0 + columns`` of float rows."""
+    require_cuda(x)
+    _floats(x)
+    if x.dim() != 2 or col0 < 0 or col0 + columns > x.shape[1]:
+        raise KernelError("silu_columns: columns of a float matrix")
+    check(library("recurrent").hb_silu_columns(ptr(x), i32(x.stride(0)), i32(col0), i32(columns), i32(x.shape[0]), stream_ptr()), "silu_columns")
+
+
 def state_scan(mode: int, conv: torch.Tensor, k_off: int, q_off: int, v_off: int, proj: torch.Tensor, decay_off: int, step_off: int,
                a_log: torch.Tensor, dt_bias: torch.Tensor, skip: torch.Tensor | None, state: torch.Tensor, state_off: int, slots: torch.Tensor,
                row_start: torch.Tensor, rows: int, heads: int, groups: int, n: int, n_padded: int, e: int, q_scale: float = 1.0,
@@ -56,6 +91,26 @@ def state_scan(mode: int, conv: torch.Tensor, k_off: int, q_off: int, v_off: int
                                              i32(decay_off), i32(step_off), ptr(a_log), ptr(dt_bias), ptr(skip), ptr(state),
                                              ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(rows),
                                              i32(heads), i32(groups), i32(n), i32(n_padded), i32(e), f32(q_scale), stream_ptr()), "state_scan")
+    return out
+
+
+def channel_delta_scan(conv: torch.Tensor, k_off: int, q_off: int, v_off: int, decay: torch.Tensor, step: torch.Tensor, step_off: int, a_log: torch.Tensor,
+                       dt_bias: torch.Tensor, state: torch.Tensor, state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, groups: int,
+                       n: int, n_padded: int, e: int, q_scale: float = 1.0) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key entry, per head:  S <- diag(g) S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q  with
+    g_i = exp(-exp(a_log) softplus(decay_i + dt_bias_i)), b = sigmoid(step), k and q made unit vectors and q times ``q_scale``.  ``conv``
+    [tokens, *] holds keys, queries and values at their offsets, ``decay`` [tokens, heads * n] the decays' pre-activations, ``step`` [tokens, *]
+    the steps' at ``step_off``; ``a_log`` has one entry per head, ``dt_bias`` one per head and key entry.  Every row's tokens walk from
+    and into its slot of ``state``.  Returns [tokens, heads * e]."""
+    require_cuda(conv, decay, step, a_log, dt_bias, state, slots, row_start)
+    _floats(conv, decay, step, a_log, dt_bias, state)
+    if a_log.numel() != heads or dt_bias.numel() != heads * n or decay.shape[1] != heads * n or not a_log.is_contiguous() or not dt_bias.is_contiguous():
+        raise KernelError("channel_delta_scan: a rate per head, a bias and a pre-activation per head and key entry")
+    out = torch.empty((conv.shape[0], heads * e), dtype=torch.float32, device=conv.device)
+    check(library("recurrent").hb_channel_delta_scan(ptr(conv), i32(conv.stride(0)), i32(k_off), i32(q_off), i32(v_off), ptr(decay), i32(decay.stride(0)), i32(0),
+                                                     ptr(step), i32(step.stride(0)), i32(step_off), ptr(a_log), ptr(dt_bias), ptr(state),
+                                                     ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(rows), i32(heads),
+                                                     i32(groups), i32(n), i32(n_padded), i32(e), f32(q_scale), stream_ptr()), "channel_delta_scan")
     return out
 
 
@@ -112,10 +167,10 @@ def tanh_rows(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight: torch.Tensor | None, group: int, gate_first: bool, eps: float,
-                     out_dtype: torch.dtype, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+                     out_dtype: torch.dtype, scale: float = 1.0, out: torch.Tensor | None = None, sigmoid_gate: bool = False) -> torch.Tensor:
     """RMS norm of ``y`` [tokens, width] in groups of ``group`` columns, times ``weight`` (indexed by column modulo its length;
-    None: no weight), gated by silu of the columns ``gate_off ..`` of ``gate``: before the norm (``gate_first``) or after it,
-    times ``scale``.  ``out``: a [tokens, >= width] view the result is written to."""
+    None: no weight), gated by silu (``sigmoid_gate``: by the sigmoid) of the columns ``gate_off ..`` of ``gate``: before the norm
+    (``gate_first``) or after it, times ``scale``.  ``out``: a [tokens, >= width] view the result is written to."""
     require_cuda(y, gate, weight, out)
     _floats(y, gate, weight)
     tokens, width = y.shape
@@ -128,7 +183,7 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight:
     check(library("recurrent").hb_gated_group_norm(ptr(y), i32(y.stride(0)), ptr(gate), i32(gate.stride(0)), i32(gate_off), ptr(weight),
                                                    i32(weight.numel() if weight is not None else 0), i32(group), i32(width // group),
                                                    i32(1 if gate_first else 0), f32(eps), f32(scale), ptr(out), i32(is_bf16(out)), i32(out.stride(0)),
-                                                   i32(tokens), stream_ptr()), "gated_group_norm")
+                                                   i32(tokens), i32(1 if sigmoid_gate else 0), stream_ptr()), "gated_group_norm")
     return out
 
 

@@ -1,4 +1,4 @@
-from . import attention, attention_capped, attention_latent, attention_sloped, block, embedding, experts, mlp, norm, parallel, recurrent, rope  # noqa: F401  (register the built-in parts)
+from . import attention, attention_capped, attention_latent, attention_rotated, attention_sloped, block, embedding, experts, mlp, norm, parallel, recurrent, rope, wrappers  # noqa: F401  (register the built-in parts)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Arrangement, BuildContext,
                    Embedding, FeedForward, Head, Mixer, Norm, PagedKV, PagedTokens, Part, PositionEncoding, RequestState, WeightSpec,
                    register_arrangement, register_embedding, register_feed_forward, register_head, register_mixer,

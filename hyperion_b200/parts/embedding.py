@@ -5,7 +5,9 @@ float, where head is ``lm_head.weight`` or, with tied embeddings, the embedding 
 (helios/crates/helios-hal/src/backends/hopper_sm90/forward.rs:45-51, session.rs:844-848).
 Parameters: ``vocab_size``, ``hidden_size``, ``weight_name`` (the tensor's name after the prefix, ``weight``
 unless stated); the embedding also ``scale`` (the looked-up row is multiplied by it in float, 1 unless
-stated); the head also ``tied`` (then it owns no tensor and is handed the embedding's table).
+stated) and ``norm_weight_name`` with ``eps`` (unless absent: the looked-up row passes an RMS norm with that weight
+before it becomes the stream); the head also ``tied`` (then it owns no tensor and is handed the embedding's table)
+and ``scale`` (the logits are multiplied by it, 1 unless stated).
 
 ``offset_table`` is a learned table [count, hidden] of vectors that the schedule adds to the stream before an entry
 runs (a model that passes some layers several times marks each pass this way).  Parameters: ``count``, ``hidden_size``,
@@ -29,18 +31,29 @@ class TokenEmbedding(Embedding):
         self.hidden = int(spec.params["hidden_size"])
         self.scale = float(spec.params.get("scale", 1.0))
         self.weight_name = str(spec.params.get("weight_name", "weight"))
+        self.norm_name = spec.params.get("norm_weight_name")
+        self.eps = float(spec.params.get("eps", 0.0))
+        self.norm_weight = None
 
     def weights(self):
-        return {self.weight_name: WeightSpec((self.vocab, self.hidden))}
+        wanted = {self.weight_name: WeightSpec((self.vocab, self.hidden))}
+        if self.norm_name is not None:
+            wanted[str(self.norm_name)] = WeightSpec((self.hidden,), init="one_plus_normal")
+        return wanted
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.table = tensors[self.weight_name].contiguous()
+        if self.norm_name is not None:
+            self.norm_weight = tensors[str(self.norm_name)].to(torch.float32).contiguous()
 
     def kernel_modules(self):
         return [("elementwise", {})]
 
     def forward(self, token_ids):
-        return ops.embedding(self.table, token_ids, scale=self.scale)
+        h = ops.embedding(self.table, token_ids, scale=self.scale)
+        if self.norm_weight is not None:  # the stream starts as the normalised row, in float
+            h = ops.add_rmsnorm(h, None, self.norm_weight, self.eps, torch.float32)
+        return h
 
     def shared_table(self):
         return self.table
@@ -53,6 +66,7 @@ class LinearHead(Head):
         self.hidden = int(spec.params["hidden_size"])
         self.tied = bool(spec.params.get("tied", False))
         self.weight_name = str(spec.params.get("weight_name", "weight"))
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight = None
 
     def weights(self):
@@ -71,10 +85,11 @@ class LinearHead(Head):
         self.weight = table
 
     def kernel_modules(self):
-        return [("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        return [("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})] + ([("elementwise", {})] if self.scale != 1.0 else [])
 
     def forward(self, x):
-        return ops.linear(x, self.weight, None, torch.float32)
+        logits = ops.linear(x, self.weight, None, torch.float32)
+        return ops.scale_(logits, self.scale) if self.scale != 1.0 else logits
 
 
 register_embedding("token_embedding", TokenEmbedding)

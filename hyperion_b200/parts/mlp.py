@@ -62,16 +62,18 @@ register_feed_forward("swiglu", SwiGLU)
 
 
 class ActivatedMLP(FeedForward):
-    """The feed-forward without a gate: down(act(up(x))), no biases, act = the tanh form of GELU.
-    Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` (``gelu_tanh``), ``names`` (``{"up": ..., "down": ...}``)."""
+    """The feed-forward without a gate: down(act(up(x))), no biases, act = the tanh form of GELU or its exact (erf) form.
+    Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` (``gelu_tanh`` or ``gelu_erf``), ``names`` (``{"up": ..., "down": ...}``)."""
+
+    ACTIVATIONS = {"gelu_tanh": "gelu_tanh", "gelu_erf": "gelu_erf"}  # the name of the activation -> the operation of ``ops``
 
     def __init__(self, spec: PartSpec, build: BuildContext):
         super().__init__(spec, build)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.activation = str(spec.params.get("activation", "gelu_tanh"))
-        if self.activation != "gelu_tanh":
-            raise ValueError(f"no activation {self.activation!r} (known: gelu_tanh)")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"no activation {self.activation!r} (known: {sorted(self.ACTIVATIONS)})")
         names = dict(spec.params.get("names") or {})
         self.up_name, self.down_name = names.get("up", "up_proj.weight"), names.get("down", "down_proj.weight")
 
@@ -85,7 +87,7 @@ class ActivatedMLP(FeedForward):
         return [("elementwise", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
 
     def forward(self, x, step):
-        act = ops.gelu_tanh(ops.linear(x, self.w_up, None, self.dtype))
+        act = getattr(ops, self.ACTIVATIONS[self.activation])(ops.linear(x, self.w_up, None, self.dtype))
         return ops.linear(act, self.w_down, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 

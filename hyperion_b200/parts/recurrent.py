@@ -38,6 +38,19 @@ is x + (x' - x) * mu_s.
 The record holds the heads' matrices, then the last token's x.  Mixes, tanh, decays, the recurrence and the norm are float.
 Parameters: ``hidden_size``, ``heads``, ``head_dim``, ``decay_rank`` (what random weights get; a checkpoint's tensors decide), ``eps``.
 Tensors: mu.r, mu.k, mu.v, mu.g, mu.w, r, k, v, g, w1, w2, w0, u, norm, o.
+
+Gated delta rule with a decay per key channel (``channel_delta``): the delta rule above with
+    g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 x) + dt_bias)), one per head and key entry;  S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    y = o / rms(o) per head, times norm (one weight of a head's size), times sigmoid(W_g2 (W_g1 x)), then W_o.
+The decay and the gate come through two small matrices each; their inner sizes are read off the tensors.
+Parameters: ``hidden_size``, ``heads``, ``kv_heads``, ``head_dim``, ``value_dim``, ``conv`` (taps), ``eps``, ``decay_rank`` and ``gate_rank`` (what
+random weights get).  Tensors: q, k, v, q.conv, k.conv, v.conv, b, a1, a2, A_log, dt_bias, g1, g2, norm, o.
+
+Lightning attention (``lightning``): a matrix state per head that fades by a constant of the head, with nothing between the projections and
+the recurrence but an activation:
+    q, k, v = silu(W_q x), silu(W_k x), silu(W_v x);  S <- decay_h S + k v^T;  o = S^T q
+    y = [all heads' o side by side] / its root mean square, times norm, times sigmoid(W_g x), then W_o.
+Parameters: ``hidden_size``, ``heads``, ``head_dim``, ``value_dim``, ``decay`` (one per head), ``eps``.  Tensors: q, k, v, g, norm, o.
 """
 from __future__ import annotations
 
@@ -283,6 +296,117 @@ class WkvMixer(Mixer):
         return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 
+class ChannelDeltaRule(_ScanMixer):
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        p = spec.params
+        self.hidden, self.heads, self.groups = int(p["hidden_size"]), int(p["heads"]), int(p["kv_heads"])
+        self.n, self.e, self.taps, self.eps = int(p["head_dim"]), int(p["value_dim"]), int(p["conv"]), float(p["eps"])
+        self.decay_rank, self.gate_rank = int(p.get("decay_rank") or 16), int(p.get("gate_rank") or 16)
+        self.qk_width, self.v_width = self.groups * self.n, self.heads * self.e
+        self.conv_channels = 2 * self.qk_width + self.v_width
+        self.beta_off = self.conv_channels  # columns of the in-projection: [q | k | v | b | a1 | g1]; the last two as wide as the tensors say
+        self._finish_layout()
+
+    def weights(self) -> dict[str, WeightSpec]:
+        h, taps = self.hidden, self.taps
+        return {"q": WeightSpec((self.qk_width, h)), "k": WeightSpec((self.qk_width, h)), "v": WeightSpec((self.v_width, h)),
+                "q.conv": WeightSpec((self.qk_width, taps)), "k.conv": WeightSpec((self.qk_width, taps)), "v.conv": WeightSpec((self.v_width, taps)),
+                "b": WeightSpec((self.heads, h)), "A_log": WeightSpec((self.heads,)), "norm": WeightSpec((self.e,), init="one_plus_normal"),
+                "a1": WeightSpec((self.decay_rank, h), any_extent=(0,)), "a2": WeightSpec((self.heads * self.n, self.decay_rank), any_extent=(1,)),
+                "dt_bias": WeightSpec((self.heads * self.n,)),
+                "g1": WeightSpec((self.gate_rank, h), any_extent=(0,)), "g2": WeightSpec((self.v_width, self.gate_rank), any_extent=(1,)),
+                "o": WeightSpec((self.hidden, self.v_width))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for first, second in (("a1", "a2"), ("g1", "g2")):
+            if tensors[first].shape[0] != tensors[second].shape[1]:
+                raise ValueError(f"the matrices {first} and {second} meet in {tensors[first].shape[0]} and {tensors[second].shape[1]} entries")
+        mats = [tensors[name] for name in ("q", "k", "v", "b", "a1", "g1")]
+        dtype = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+        self.w_in = torch.cat([m.to(dtype) for m in mats], dim=0).contiguous()
+        self.decay_rank, self.gate_rank = int(tensors["a1"].shape[0]), int(tensors["g1"].shape[0])
+        self.a1_off = self.beta_off + self.heads
+        self.g1_off = self.a1_off + self.decay_rank
+        self.w_a2, self.w_g2 = tensors["a2"].contiguous(), tensors["g2"].contiguous()
+        self.w_conv = torch.cat([self._float(tensors[name]) for name in ("q.conv", "k.conv", "v.conv")], dim=0).contiguous()
+        self.a_log, self.dt_bias = self._float(tensors["A_log"]), self._float(tensors["dt_bias"])
+        self.norm = self._float(tensors["norm"])
+        self.w_o = tensors["o"].contiguous()
+
+    def forward(self, x, step, cache, own_cache):
+        if cache is None or not own_cache:
+            raise ValueError("the delta rule keeps a state per request; the schedule gave it none")
+        proj = ops.linear(x, self.w_in, None, torch.float32)
+        state, slots, rows = cache.state, cache.slots, step.n_rows
+        conv = recurrent.causal_conv_silu(proj, 0, self.w_conv, None, state, self.conv_off, slots, step.token_row, step.row_start)
+        recurrent.conv_state_update(proj, 0, self.conv_channels, self.taps, state, self.conv_off, slots, step.row_start, rows)
+        decay = ops.linear(proj[:, self.a1_off : self.a1_off + self.decay_rank], self.w_a2, None, torch.float32)
+        gate = ops.linear(proj[:, self.g1_off : self.g1_off + self.gate_rank], self.w_g2, None, torch.float32)
+        o = recurrent.channel_delta_scan(conv, self.qk_width, 0, 2 * self.qk_width, decay, proj, self.beta_off, self.a_log, self.dt_bias, state, 0, slots,
+                                         step.row_start, rows, self.heads, self.groups, self.n, self.n_padded, self.e, q_scale=self.n ** -0.5)
+        y = recurrent.gated_group_norm(o, gate, 0, self.norm, self.e, False, self.eps, self.dtype, sigmoid_gate=True)
+        return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
+class LightningAttention(Mixer):
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        p = spec.params
+        self.hidden, self.heads = int(p["hidden_size"]), int(p["heads"])
+        self.n, self.e, self.eps = int(p["head_dim"]), int(p.get("value_dim") or p["head_dim"]), float(p["eps"])
+        decay = [float(d) for d in p["decay"]]
+        if len(decay) != self.heads:
+            raise ValueError(f"{len(decay)} decays for {self.heads} heads")
+        if self.n > 256:
+            raise ValueError(f"a state of {self.n} per column is above the scan kernel's limit of 256")
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(build.device)
+        self.qk_width, self.v_width = self.heads * self.n, self.heads * self.e
+        self.n_padded = _round_up(self.n, 4)
+        self.record = self.heads * self.e * self.n_padded
+
+    def weights(self) -> dict[str, WeightSpec]:
+        h = self.hidden
+        return {"q": WeightSpec((self.qk_width, h)), "k": WeightSpec((self.qk_width, h)), "v": WeightSpec((self.v_width, h)), "g": WeightSpec((self.v_width, h)),
+                "norm": WeightSpec((self.v_width,), init="one_plus_normal"), "o": WeightSpec((h, self.v_width))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        mats = [tensors[name] for name in ("q", "k", "v", "g")]
+        dtype = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+        self.w_in = torch.cat([m.to(dtype) for m in mats], dim=0).contiguous()  # columns of the in-projection: [q | k | v | g]
+        self.norm = tensors["norm"].to(torch.float32).contiguous()
+        self.w_o = tensors["o"].contiguous()
+
+    def cache_request(self):
+        return RequestState((self.record,), torch.float32)
+
+    def kernel_modules(self):
+        return [("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+
+    def step_plans(self):
+        return recurrent.segment_planner(self.dtype)
+
+    def forward(self, x, step, cache, own_cache):
+        if cache is None or not own_cache:
+            raise ValueError("lightning attention keeps a state per request; the schedule gave it none")
+        proj = ops.linear(x, self.w_in, None, torch.float32)
+        k_off, v_off = self.qk_width, 2 * self.qk_width
+        recurrent.silu_columns_(proj, 0, v_off + self.v_width)
+        # long rows in segments while one pass leaves the GPU mostly idle, as for the package's other constant-decay recurrence
+        blocks = self.heads * -(-self.e // 32)
+        segments = step.host.get("scan_segments", 0) if self.dtype == torch.bfloat16 and blocks <= 100 else 0
+        if segments:
+            o = recurrent.retention_in_segments(proj, k_off, 0, v_off, self.decay, cache.state, cache.slots, step.extra["scan_seg_start"],
+                                                step.extra["scan_seg_row"], segments, self.heads, self.n, self.n_padded, self.e)
+        else:
+            o = recurrent.state_scan(recurrent.MODE_RETENTION, proj, k_off, 0, v_off, proj, 0, 0, self.decay, self.decay, None, cache.state, 0, cache.slots,
+                                     step.row_start, step.n_rows, self.heads, self.heads, self.n, self.n_padded, self.e)
+        y = recurrent.gated_group_norm(o, proj, v_off + self.v_width, self.norm, self.v_width, False, self.eps, self.dtype, sigmoid_gate=True)
+        return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
+register_mixer("channel_delta", ChannelDeltaRule)
+register_mixer("lightning", LightningAttention)
 register_mixer("delta_rule", GatedDeltaRule)
 register_mixer("mamba1", SelectiveScanMixer)
 register_mixer("mamba2", StateSpaceMixer)
