@@ -835,6 +835,173 @@ def kudazen_workload(args) -> int:
     return 0
 
 
+TOBADRA_SIZES = {
+    # width; window attention (heads, kv heads, head size, window, rotated entries of queries and keys); lightning (heads, key size, value
+    # size); delta rule with a decay per key channel (heads, key size, value size, inner size of decay and gate); dense feed-forward; experts
+    # (count, identities, per token, inner width, shared inner width, groups, groups kept).  Eight layer runs A+dense A+experts L+experts
+    # D+experts A+experts A+experts L+experts D+experts, the last with the tensors of the fourth; 32,000 tokens
+    "2k": {"width": 2048, "attention": (16, 4, 128, 1024, 64), "lightning": (16, 128, 128), "delta": (16, 128, 128, 64), "ff": 8192,
+           "experts": (16, 2, 2, 2048, 2048, 6, 4)},
+    "4k": {"width": 4096, "attention": (32, 8, 128, 2048, 64), "lightning": (32, 128, 128), "delta": (32, 128, 128, 64), "ff": 14336,
+           "experts": (16, 2, 2, 3584, 3584, 6, 4)},
+}
+
+
+def tobadra_document(size: dict, vocab: int = 32000) -> dict:
+    heads, kv_heads, dim, window, rot = size["attention"]
+    count, identity, top, inner, shared, groups, keep = size["experts"]
+    experts = {"kind": "moe", "expert": {"ff": inner}, "router": {"experts": count, "top": top, "scale": 2.5, "identity": identity, "groups": {"count": groups, "keep": keep}},
+               "shared": {"ff": shared}}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window}, "rot": {"dims": rot, "base": 1e6}}
+    l_heads, l_dim, l_vdim = size["lightning"]
+    lightning = {"heads": l_heads, "dim": l_dim, "vdim": l_vdim, "decay": [1.0 - 2.0 ** (-5 - 3 * i / l_heads) for i in range(l_heads)]}
+    d_heads, d_dim, d_vdim, rank = size["delta"]
+    delta = {"heads": d_heads, "kv_heads": d_heads, "dim": d_dim, "vdim": d_vdim, "conv": 4, "decay_rank": rank, "gate_rank": rank}
+    layers = [{"type": "attention", "mixer": attention, "mlp": {"kind": "dense", "ff": size["ff"]}}, {"type": "attention", "mixer": attention, "mlp": experts},
+              {"type": "lightning", "mixer": lightning, "mlp": experts}, {"type": "channel_delta", "mixer": delta, "mlp": experts},
+              {"type": "attention", "mixer": attention, "mlp": experts}, {"type": "attention", "mixer": attention, "mlp": experts},
+              {"type": "lightning", "mixer": lightning, "mlp": experts}, {"type": "channel_delta", "mixer": delta, "mlp": experts, "weights_of": 3}]
+    return {"architecture": "Tobadra", "vocab": vocab, "width": size["width"], "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "logit_scale": 1.0, "layers": layers}
+
+
+def tobadra_kernels(size: dict, measured: dict) -> dict:
+    """The design's own kernels alone at this size, a prompt of 2,048 tokens in one row and 8 rows of one decoded token behind 2,048: time, the
+    bytes each must move against the measured copy bandwidth, for the scans the float32 operations; beside each the like kernel of the
+    closest models (Mirovik's router, sum and retention; Nunivik's delta rule and convolution)."""
+    import torch
+
+    from hyperion_b200 import ops
+    from hyperion_b200.ops import moe, recurrent
+
+    dev = torch.device("cuda")
+    hbm = measured["hbm_gbs"] * 1e9
+    out: dict = {}
+    width = size["width"]
+
+    def report(name, ms, bytes_moved, fp32_flops=None):
+        entry = {"us": round(ms * 1e3, 2), "bytes": int(bytes_moved), "of_measured_bandwidth": round(bytes_moved / (ms / 1e3) / hbm, 3)}
+        if fp32_flops is not None:
+            entry["fp32_tflops"] = round(fp32_flops / (ms / 1e3) / 1e12, 2)
+        out[name] = entry
+
+    for shape, counts, before in (("prefill_2048", [PROMPT], 0), ("decode_8", [1] * 8, PROMPT)):
+        tokens, rows = sum(counts), len(counts)
+        starts = [0]
+        for c in counts:
+            starts.append(starts[-1] + c)
+        row_start = torch.tensor(starts, dtype=torch.int32, device=dev)
+        token_row = torch.tensor([r for r, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=dev)
+        slots = torch.arange(rows, dtype=torch.int32, device=dev)
+        positions = torch.cat([torch.arange(c, dtype=torch.int32) + before for c in counts]).to(dev)
+        # the convolution every mixer reads through, its state, and the gate on a sublayer's result
+        x = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+        w_canon = torch.randn(width, 4, device=dev) * 0.3
+        kept = torch.zeros(rows, 3 * width, device=dev)
+        report(f"residual_conv/{shape}", timed(lambda: recurrent.residual_conv(x, w_canon, kept, 0, slots, token_row, row_start)), tokens * width * 4)
+        report(f"conv_state_keep/{shape}", timed(lambda: recurrent.conv_state_keep(x, 4, kept, 0, slots, row_start, rows)), rows * 3 * width * 6)
+        wide = torch.randn(tokens, width, device=dev)
+        report(f"nunivik.conv_silu/{shape}", timed(lambda: recurrent.causal_conv_silu(wide, 0, w_canon, None, kept, 0, slots, token_row, row_start)), tokens * width * 8)
+        gate = torch.randn(tokens, width, device=dev)
+        y = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+        report(f"sigmoid_gate/{shape}", timed(lambda: ops.sigmoid_gate_(y, gate, 0)), tokens * width * 8)
+        # the values' rotation and the result's rotation back, beside the rotation of queries and keys with the cache write
+        heads, kv_heads, dim, _, rot = size["attention"]
+        proj = torch.randn(tokens, (heads + 2 * kv_heads) * dim, device=dev)
+        freq_v, freq_qk = torch.rand(dim // 2, device=dev), torch.rand(rot // 2, device=dev)
+        report(f"rotate_values/{shape}", timed(lambda: ops.rotate_heads_(proj, (heads + kv_heads) * dim, kv_heads, dim, positions, freq_v, dim, True, 1.0)), tokens * kv_heads * dim * 8)
+        attn = torch.randn(tokens, heads * dim, device=dev).to(torch.bfloat16)
+        report(f"rotate_result_back/{shape}", timed(lambda: ops.rotate_heads_(attn, 0, heads, dim, positions, freq_v, dim, True, -1.0)), tokens * heads * dim * 4)
+        q = torch.empty(tokens, heads * dim, dtype=torch.bfloat16, device=dev)
+        k = torch.empty(tokens, kv_heads * dim, dtype=torch.bfloat16, device=dev)
+        report(f"mirovik.rotate_q_k/{shape}", timed(lambda: ops.heads_prepare_wide(proj, 0, heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim, dim, positions, q_out=q, k_out=k,
+                                                                                inv_freq=freq_qk, rot_dims=rot, rot_half=True)), tokens * (heads + kv_heads) * dim * 6)
+        # the two recurrences and their gated norms; the like kernels: the delta rule with one decay per head, the same scan as retention
+        d_heads, n, e, rank = size["delta"]
+        conv = torch.randn(tokens, 2 * d_heads * n + d_heads * e, device=dev) * 0.5
+        decay_in, step_in = torch.randn(tokens, d_heads * n, device=dev), torch.randn(tokens, 2 * d_heads, device=dev)
+        a_log, dt_bias, dt_head = torch.zeros(d_heads, device=dev), torch.zeros(d_heads * n, device=dev), torch.zeros(d_heads, device=dev)
+        state = torch.zeros(rows, d_heads * e * n, device=dev)
+        scan_bytes = 4 * (tokens * (3 * d_heads * n + 2 * d_heads * e) + 2 * rows * d_heads * e * n)
+        report(f"channel_delta.scan/{shape}", timed(lambda: recurrent.channel_delta_scan(conv, d_heads * n, 0, 2 * d_heads * n, decay_in, step_in, 0, a_log, dt_bias, state, 0, slots,
+                                                                                      row_start, rows, d_heads, d_heads, n, n, e, q_scale=n ** -0.5)),
+               scan_bytes, fp32_flops=7.0 * tokens * d_heads * n * e)
+        report(f"nunivik.delta_scan/{shape}", timed(lambda: recurrent.state_scan(recurrent.MODE_DELTA, conv, d_heads * n, 0, 2 * d_heads * n, step_in, d_heads, 0, a_log, dt_head, None,
+                                                                              state, 0, slots, row_start, rows, d_heads, d_heads, n, n, e, q_scale=n ** -0.5)),
+               scan_bytes - 4 * tokens * d_heads * n, fp32_flops=6.0 * tokens * d_heads * n * e)
+        o = torch.randn(tokens, d_heads * e, device=dev)
+        g_in = torch.randn(tokens, d_heads * e, device=dev)
+        norm_head, norm_all = torch.ones(e, device=dev), torch.ones(d_heads * e, device=dev)
+        report(f"channel_delta.gated_norm/{shape}", timed(lambda: recurrent.gated_group_norm(o, g_in, 0, norm_head, e, False, 1e-6, torch.bfloat16, sigmoid_gate=True)),
+               tokens * d_heads * e * 10)
+        l_heads, ln, le = size["lightning"]
+        qkv = torch.randn(tokens, 2 * l_heads * ln + 2 * l_heads * le, device=dev)
+        report(f"lightning.silu/{shape}", timed(lambda: recurrent.silu_columns_(qkv, 0, 2 * l_heads * ln + l_heads * le)), tokens * (2 * l_heads * ln + l_heads * le) * 8)
+        l_decay = torch.full((l_heads,), 0.99, device=dev)
+        l_state = torch.zeros(rows, l_heads * le * ln, device=dev)
+        l_bytes = 4 * (tokens * (2 * l_heads * ln + 2 * l_heads * le) + 2 * rows * l_heads * le * ln)
+        report(f"lightning.scan/{shape}", timed(lambda: recurrent.state_scan(recurrent.MODE_RETENTION, qkv, l_heads * ln, 0, 2 * l_heads * ln, qkv, 0, 0, l_decay, l_decay, None, l_state, 0,
+                                                                          slots, row_start, rows, l_heads, l_heads, ln, ln, le)), l_bytes, fp32_flops=4.0 * tokens * l_heads * ln * le)
+        cut = recurrent.plan_segments(counts)
+        if cut is not None:  # the long row in segments side by side, as the bfloat16 engine walks it
+            seg_start, seg_row = torch.tensor(cut[0], dtype=torch.int32, device=dev), torch.tensor(cut[1], dtype=torch.int32, device=dev)
+            report(f"lightning.scan_in_segments/{shape}", timed(lambda: recurrent.retention_in_segments(qkv, l_heads * ln, 0, 2 * l_heads * ln, l_decay, l_state, slots, seg_start, seg_row,
+                                                                                                         len(cut[1]), l_heads, ln, ln, le)), l_bytes, fp32_flops=8.0 * tokens * l_heads * ln * le)
+        lo = torch.randn(tokens, l_heads * le, device=dev)
+        report(f"lightning.gated_norm_over_all_heads/{shape}", timed(lambda: recurrent.gated_group_norm(lo, qkv, 2 * l_heads * ln + l_heads * le, norm_all[: l_heads * le], l_heads * le, False,
+                                                                                                     1e-6, torch.bfloat16, sigmoid_gate=True)), tokens * l_heads * le * 10)
+        report(f"mirovik.gated_norm_per_head/{shape}", timed(lambda: recurrent.gated_group_norm(lo, qkv, 2 * l_heads * ln + l_heads * le, None, le, False, 1e-6, torch.bfloat16)),
+               tokens * l_heads * le * 10)
+        # experts: the router with scores, correction and groups, the plan, the activation, the weighted sum; beside Mirovik's router and sum
+        count, identity, top, inner, _, groups, keep = size["experts"]
+        outputs = count + identity
+        router, correction = torch.randn(outputs, width, device=dev) * 0.05, torch.randn(outputs, device=dev) * 0.05
+        report(f"experts.route_scored/{shape}", timed(lambda: moe.route_scored(x, router, correction, top, groups, keep, 2.5)), tokens * width * 2 + outputs * width * 4)
+        report(f"mirovik.route/{shape}", timed(lambda: moe.route(x, router[:count].contiguous(), top)), tokens * width * 2 + count * width * 4)
+        chosen, weights = moe.route_scored(x, router, correction, top, groups, keep, 2.5)
+        where = moe.plan(chosen, None, count)
+        up = torch.randn(where.capacity, inner, device=dev).to(torch.bfloat16)
+        report(f"experts.gelu_erf/{shape}", timed(lambda: ops.gelu_erf(up)), where.capacity * inner * 4)
+        report(f"mirovik.gelu_tanh/{shape}", timed(lambda: ops.gelu_tanh(up)), where.capacity * inner * 4)
+        z = torch.randn(where.capacity, width, device=dev).to(torch.bfloat16)
+        base, base_gate = torch.randn(tokens, width, device=dev).to(torch.bfloat16), torch.randn(tokens, device=dev)
+        report(f"experts.combine_weighted/{shape}", timed(lambda: moe.combine_weighted(z, where, weights, x, base, base_gate)), tokens * (top + 3) * width * 2)
+        plain_where = moe.plan(chosen.clamp(max=count - 1), weights, count)
+        report(f"mirovik.combine/{shape}", timed(lambda: moe.combine(z, plain_where, base, tokens)), tokens * (top + 2) * width * 2)
+    return out
+
+
+def tobadra_workload(args) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 from a context of 2,048) of the Tobadra design at two sizes that
+    resemble real layers, beside the closest model of the package, Mirovik (sublayers normalised on both sides, experts, a constant-decay
+    recurrence), at equal width and number of layer runs; random weights."""
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import MirovikConfig, TobadraConfig
+
+    measured, kind = peaks()
+    for name, size in TOBADRA_SIZES.items():
+        if args.size and name != args.size:
+            continue
+        arms = {"tobadra": ("Tobadra", TobadraConfig.from_dict(tobadra_document(size))),
+                "mirovik": ("Mirovik", MirovikConfig.from_dict(mirovik_document(MIROVIK_SIZES[name])))}
+        line = {"workload": "tobadra", "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
+                "layers": "A+dense A+experts L+experts D+experts A+experts A+experts L+experts D+experts beside (P+dense P+experts S+dense P+experts) x 2", "peaks": kind}
+        for arm, (architecture, config) in arms.items():
+            engine = Engine.from_random(architecture, config, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (PROMPT + 256), max_requests=8)
+            prefill = time_prefill(engine)
+            decode = time_decode(engine, 8, 16, max(3, args.warmup), decode_tokens=max(3, args.warmup) + 160)
+            line[arm] = {"prefill_ms": round(prefill["ms"], 3), "prefill_tokens_per_s": round(PROMPT / prefill["ms"] * 1e3),
+                         "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tok_s"], 1),
+                         "decode_launches_per_step": round(decode["launches"] / decode["steps"], 1)}
+            del engine
+            torch.cuda.empty_cache()
+        if not args.skip_points:
+            line["kernels"] = tobadra_kernels(size, measured)
+        print(json.dumps(line), flush=True)
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -847,13 +1014,13 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
-    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik", "mirovik", "kudazen"],
+    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik", "mirovik", "kudazen", "tobadra"],
                         help="one of the other workloads instead: 128 requests with prompts of 16..4096 tokens and 256 decoded tokens "
                              "each through generate() at the 1.5B shape; batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape; "
                              "or the reference's own published tables (decode by batch at context 512, prefill by length) at the 0.5B and 7B shapes; "
                              "or the Nunivik design at two layer sizes beside the Qwen2 model of equal size, with its own kernels timed alone; "
                              "or the Mirovik design at two layer sizes beside the Nunivik model of equal size, likewise")
-    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik, mirovik or kudazen: one of its sizes only")
+    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik, mirovik, kudazen or tobadra: one of its sizes only")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -865,6 +1032,8 @@ def main() -> int:
         return mirovik_workload(args)
     if args.workload == "kudazen":
         return kudazen_workload(args)
+    if args.workload == "tobadra":
+        return tobadra_workload(args)
     if args.workload:
         return other_workload(args.workload)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

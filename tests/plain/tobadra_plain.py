@@ -221,7 +221,7 @@ def forward(config: dict, weights: dict[str, torch.Tensor], token_ids, dtype=tor
         p = f"l{source}."
         m = layer["mixer"]
         a = rms_norm(x, w[p + "norm1"], eps)
-        read = a + causal_conv(a, w[p + "canon1"])
+        read = a + causal_conv(a, w[p + "canon1"]) if config.get("canon") is not None else a
         if layer["type"] == "attention":
             y = window_attention(read, w, p + "mix.", m)
         elif layer["type"] == "lightning":
