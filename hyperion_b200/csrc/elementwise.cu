@@ -672,21 +672,26 @@ HB_EXPORT int hb_stream_copy(const float* h, void* copy, long long count, cudaSt
 // sublayer boundary:   h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w_post (+ offset);   out[i] = h[t] / sqrt(mean(h[t]^2) + eps) * w_next.
 // Every piece is optional: without y only the offset is added, without w_next nothing is normalised for a reader.  With `rows`
 // only the listed rows are worked on and h is left as it was (the last norm of a model, where only some rows are read).
+// With `gate` [tokens, gate_stride] (float) the sublayer's output is first multiplied, entry by entry, by sigmoid(gate[t]): a block whose
+// sublayers are gated by a projection of what they read hands the projection on instead of launching the product itself.
 // Everything is float; sums of squares are taken in a fixed order per row.
 template <typename TY, typename TO>
 __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict__ y, const float* __restrict__ w_post,
                                      const float* __restrict__ offset, const float* __restrict__ w_next, TO* __restrict__ out,
-                                     const int* __restrict__ rows, int hidden, float eps_post, float eps_next) {
+                                     const int* __restrict__ rows, int hidden, float eps_post, float eps_next, const float* __restrict__ gate,
+                                     int gate_stride) {
     extern __shared__ float row_values[];
     __shared__ float scratch[32];
     const int i = blockIdx.x, t = rows ? rows[i] : i;
     float* hrow = h + (size_t)t * hidden;
     const TY* yrow = y ? y + (size_t)t * hidden : nullptr;
+    const float* grow = (y && gate) ? gate + (size_t)t * gate_stride : nullptr;
     float inv_y = 0.f;
     if (yrow) {
         float sum = 0.f;
         for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-            const float v = to_float(yrow[j]);
+            float v = to_float(yrow[j]);
+            if (grow) v *= 1.0f / (1.0f + expf(-grow[j]));
             sum = fmaf(v, v, sum);
         }
         inv_y = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + eps_post);
@@ -694,7 +699,7 @@ __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict
     float sum = 0.f;
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         float v = hrow[j];
-        if (yrow) v += to_float(yrow[j]) * inv_y * w_post[j];
+        if (yrow) v += to_float(yrow[j]) * (grow ? 1.0f / (1.0f + expf(-grow[j])) : 1.f) * inv_y * w_post[j];
         if (offset) v += offset[j];
         row_values[j] = v;
         if (!rows) hrow[j] = v;
@@ -709,7 +714,8 @@ __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict
 // in registers through both norms (one trip to memory), with 16-byte accesses.
 __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, const float* __restrict__ w_post,
                                             const float* __restrict__ offset, const float* __restrict__ w_next, __nv_bfloat16* __restrict__ out,
-                                            const int* __restrict__ rows, int hidden, float eps_post, float eps_next) {
+                                            const int* __restrict__ rows, int hidden, float eps_post, float eps_next, const float* __restrict__ gate,
+                                            int gate_stride) {
     __shared__ float scratch[32];
     const int i = blockIdx.x, t = rows ? rows[i] : i, j = threadIdx.x * 8;
     const bool active = j < hidden;
@@ -723,6 +729,13 @@ __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bf
             for (int k = 0; k < 4; ++k) {
                 const float2 f = __bfloat1622float2(pairs[k]);
                 v[2 * k] = f.x; v[2 * k + 1] = f.y;
+            }
+            if (gate) {
+                const float* grow = gate + (size_t)t * gate_stride + j;
+                const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
+                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] *= 1.0f / (1.0f + expf(-g[k]));
             }
         }
         float sum = 0.f;
@@ -767,15 +780,16 @@ __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bf
 }
 
 HB_EXPORT int hb_norm_add_norm(float* h, const void* y, int y_is_bf16, const float* w_post, const float* offset, const float* w_next, void* out,
-                               int out_is_bf16, const int* rows, int n_rows, int hidden, float eps_post, float eps_next, cudaStream_t stream) {
+                               int out_is_bf16, const int* rows, int n_rows, int hidden, float eps_post, float eps_next, const float* gate,
+                               int gate_stride, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (hidden <= 0 || hidden > 49152 || (y && !w_post) || (w_next && !out)) return HB_BAD_ARGUMENT;
     const bool halves = (!y || y_is_bf16) && (!w_next || out_is_bf16);
-    if (halves && hidden % 8 == 0 && hidden <= 8192 &&
-        (((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)offset | (uintptr_t)w_next | (uintptr_t)out) & 15) == 0) {
+    if (halves && hidden % 8 == 0 && hidden <= 8192 && (!gate || gate_stride % 4 == 0) &&
+        (((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)offset | (uintptr_t)w_next | (uintptr_t)out | (uintptr_t)gate) & 15) == 0) {
         const int lanes = ((hidden / 8 + 31) / 32) * 32;  // which kernel runs follows from the width and the types alone
         norm_add_norm_bf16x8_kernel<<<n_rows, lanes, 0, stream>>>(h, (const __nv_bfloat16*)y, w_post, offset, w_next, (__nv_bfloat16*)out, rows, hidden,
-                                                                  eps_post, eps_next);
+                                                                  eps_post, eps_next, gate, gate_stride);
         return launch_status();
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -784,7 +798,7 @@ HB_EXPORT int hb_norm_add_norm(float* h, const void* y, int y_is_bf16, const flo
     do {                                                                                                                                  \
         if (shared > 48 * 1024) cudaFuncSetAttribute(norm_add_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared); \
         norm_add_norm_kernel<TY, TO><<<n_rows, threads, shared, stream>>>(h, (const TY*)y, w_post, offset, w_next, (TO*)out, rows, hidden,   \
-                                                                         eps_post, eps_next);                                            \
+                                                                         eps_post, eps_next, gate, gate_stride);                         \
     } while (0)
     const bool y16 = y && y_is_bf16, o16 = w_next && out_is_bf16;
     if (y16 && o16) HB_NORM_ADD_NORM(__nv_bfloat16, __nv_bfloat16);

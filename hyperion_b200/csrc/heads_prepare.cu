@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
     int rot_dims, int rot_half, const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride,
     TO* __restrict__ k_cache, TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps,
-    const float* __restrict__ q_head_scale, int* status) {
+    const float* __restrict__ q_head_scale, const float* __restrict__ v_inv_freq, int v_rot_dims, int v_rot_half, int* status) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, head = blockIdx.y;  // q heads, then k heads, then v heads
     const int pos = positions[t];
@@ -179,7 +179,16 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
             inv = 1.0f / sqrtf(block_sum(sum, scratch) / (float)v_dim + v_unit_eps);
         }
         if (!dst) return;
-        for (int i = threadIdx.x; i < v_dim; i += THREADS) dst[i] = from_float<TO>(p[i] * inv);
+        const int v_pairs = v_inv_freq ? v_rot_dims / 2 : 0;  // a value may be stored turned by its own position
+        for (int i = threadIdx.x; i < v_pairs; i += THREADS) {
+            const int a = v_rot_half ? i : 2 * i, b = v_rot_half ? i + v_pairs : 2 * i + 1;
+            float s, c;
+            sincosf((float)pos * v_inv_freq[i], &s, &c);
+            const float u = p[a] * inv, v = p[b] * inv;
+            dst[a] = from_float<TO>(u * c - v * s);
+            dst[b] = from_float<TO>(v * c + u * s);
+        }
+        for (int i = 2 * v_pairs + threadIdx.x; i < v_dim; i += THREADS) dst[i] = from_float<TO>(p[i] * inv);
     }
 }
 }  // namespace
@@ -221,14 +230,17 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims, int rot_half,
     const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride, TO* __restrict__ k_cache,
     TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride, const int* __restrict__ block_table, int table_width,
-    const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps, const float* __restrict__ q_head_scale, int* status) {
+    const int* __restrict__ token_row, int page_size, int pages, float v_unit_eps, const float* __restrict__ q_head_scale,
+    const float* __restrict__ v_inv_freq, int v_rot_dims, int v_rot_half, int* status) {
     __shared__ float scratch[32];
-    __shared__ float cs[MAX_PAIRS], sn[MAX_PAIRS];
+    __shared__ float cs[MAX_PAIRS], sn[MAX_PAIRS], vcs[MAX_PAIRS], vsn[MAX_PAIRS];
     const int t = blockIdx.x;
     const int pos = positions[t];
     const float* row = x + (size_t)t * stride;
     const int pairs = inv_freq ? rot_dims / 2 : 0;
+    const int v_pairs = (v_inv_freq && k_cache) ? v_rot_dims / 2 : 0;  // a value may be stored turned by its own position
     for (int i = threadIdx.x; i < pairs; i += TOKEN_THREADS) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    for (int i = threadIdx.x; i < v_pairs; i += TOKEN_THREADS) sincosf((float)pos * v_inv_freq[i], &vsn[i], &vcs[i]);
     float inv_q = 1.f, inv_k = 1.f;
     if (q_norm) {
         float sum = 0.f;
@@ -274,8 +286,16 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
             }
         } else if (page >= 0) {
             TO* value_page = v_cache + (size_t)page * page_stride + (size_t)slot * token_stride;
-            for (int item = threadIdx.x; item < k_count * v_dim; item += TOKEN_THREADS) {
-                const int head = k_first + item / v_dim, d = item % v_dim;
+            for (int item = threadIdx.x; item < k_count * v_pairs; item += TOKEN_THREADS) {
+                const int head = k_first + item / v_pairs, i = item % v_pairs;
+                const int a = v_rot_half ? i : 2 * i, b = v_rot_half ? i + v_pairs : 2 * i + 1;
+                const float* p = row + v_off + (size_t)head * v_dim;
+                value_page[(size_t)head * head_stride + a] = from_float<TO>(p[a] * vcs[i] - p[b] * vsn[i]);
+                value_page[(size_t)head * head_stride + b] = from_float<TO>(p[b] * vcs[i] + p[a] * vsn[i]);
+            }
+            const int rest = v_dim - 2 * v_pairs;
+            for (int item = threadIdx.x; item < k_count * rest; item += TOKEN_THREADS) {
+                const int head = k_first + item / rest, d = 2 * v_pairs + item % rest;
                 value_page[(size_t)head * head_stride + d] = from_float<TO>(row[v_off + (size_t)head * v_dim + d]);
             }
         }
@@ -293,12 +313,14 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                     int rot_half, const int* positions, float k_scale, void* q_out, int q_out_stride, void* k_out, int k_out_stride,
                                     int out_is_bf16, void* k_cache, void* v_cache, long long page_stride, long long head_stride, int token_stride,
                                     const int* block_table, int table_width, const int* token_row, int page_size, int pages, float v_unit_eps,
-                                    const float* q_head_scale, int* status, cudaStream_t stream) {
+                                    const float* q_head_scale, const float* v_inv_freq, int v_rot_dims, int v_rot_half, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1) || !q_out || (!k_cache && !k_out)) return HB_UNSUPPORTED_SIZE;
+    if (!v_inv_freq) v_rot_dims = 0;
+    if (v_rot_dims < 0 || v_rot_dims > v_dim || (v_rot_dims & 1) || (v_rot_dims && (!k_cache || v_unit_eps >= 0.f))) return HB_UNSUPPORTED_SIZE;
     const int heads = q_heads + kv_heads + (k_cache ? kv_heads : 0);
     if (heads <= 0 || heads > 65535) return HB_UNSUPPORTED_SIZE;
-    if ((norm_whole || (!q_norm && !k_norm)) && rot_dims / 2 <= MAX_PAIRS) {  // one block per token, several when the tokens are few
+    if ((norm_whole || (!q_norm && !k_norm)) && rot_dims / 2 <= MAX_PAIRS && v_rot_dims / 2 <= MAX_PAIRS) {  // one block per token, several when the tokens are few
         const int most = q_heads > kv_heads ? q_heads : kv_heads;
         int parts = tokens >= 256 ? 1 : 256 / tokens;
         parts = parts > most ? most : (parts > 16 ? 16 : parts);
@@ -308,13 +330,13 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                              (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                              (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width,
-                                                                             token_row, page_size, pages, v_unit_eps, q_head_scale, status);
+                                                                             token_row, page_size, pages, v_unit_eps, q_head_scale, v_inv_freq, v_rot_dims, v_rot_half, status);
         else
             heads_prepare_token_kernel<<<token_grid, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                              (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                              (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size,
-                                                                             pages, v_unit_eps, q_head_scale, status);
+                                                                             pages, v_unit_eps, q_head_scale, v_inv_freq, v_rot_dims, v_rot_half, status);
         return launch_status();
     }
     const dim3 grid(tokens, heads);
@@ -323,13 +345,13 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
                                                                 eps, inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                 (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                 (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width, token_row,
-                                                                page_size, pages, v_unit_eps, q_head_scale, status);
+                                                                page_size, pages, v_unit_eps, q_head_scale, v_inv_freq, v_rot_dims, v_rot_half, status);
     else
         heads_prepare_wide_kernel<<<grid, THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, norm_whole,
                                                                 eps, inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                 (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                 (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size, pages,
-                                                                v_unit_eps, q_head_scale, status);
+                                                                v_unit_eps, q_head_scale, v_inv_freq, v_rot_dims, v_rot_half, status);
     return launch_status();
 }
 

@@ -341,6 +341,36 @@ __global__ void moe_combine_weighted_kernel(const T* __restrict__ y, const int* 
         out[(size_t)t * hidden + i] = from_float<T>(sum);
     }
 }
+
+// The same for bfloat16 rows that are whole 16-byte pieces: eight values per thread and access.
+__global__ void moe_combine_weighted_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_of, const float* __restrict__ weights,
+                                                   int top, const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ base,
+                                                   const float* __restrict__ base_gate, __nv_bfloat16* __restrict__ out, int hidden) {
+    const int t = blockIdx.x;
+    const float share = base ? (base_gate ? 1.0f / (1.0f + expf(-base_gate[t])) : 1.f) : 0.f;
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (base) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(base + (size_t)t * hidden + i);
+            const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(in[j]); sum[2 * j] = share * f.x; sum[2 * j + 1] = share * f.y; }
+        }
+        for (int k = 0; k < top; ++k) {
+            const int slot = slot_of[(size_t)t * top + k];
+            const float w = weights[(size_t)t * top + k];
+            const uint4 raw = *reinterpret_cast<const uint4*>(slot >= 0 ? y + (size_t)slot * hidden + i : x + (size_t)t * x_stride + i);
+            const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(in[j]); sum[2 * j] = fmaf(w, f.x, sum[2 * j]); sum[2 * j + 1] = fmaf(w, f.y, sum[2 * j + 1]); }
+        }
+        uint4 packed;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(sum[2 * j], sum[2 * j + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)t * hidden + i) = packed;
+    }
+}
 }  // namespace
 
 HB_EXPORT int hb_moe_route_scored(const void* x, int is_bf16, int x_stride, const float* router, const float* correction, int tokens, int hidden,
@@ -370,6 +400,11 @@ HB_EXPORT int hb_moe_combine_weighted(const void* y, const int* slot_of, const f
     if (tokens <= 0) return 0;
     if (!weights || !x || top <= 0) return HB_BAD_ARGUMENT;
     const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16 && hidden % 8 == 0 && x_stride % 8 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)base | (uintptr_t)out) & 15) == 0) {
+        moe_combine_weighted_bf16x8_kernel<<<tokens, hidden >= 2048 ? 256 : 128, 0, stream>>>((const __nv_bfloat16*)y, slot_of, weights, top, (const __nv_bfloat16*)x,
+                                                                                             x_stride, (const __nv_bfloat16*)base, base_gate, (__nv_bfloat16*)out, hidden);
+        return launch_status();
+    }
     if (is_bf16)
         moe_combine_weighted_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)y, slot_of, weights, top, (const __nv_bfloat16*)x, x_stride,
                                                                     (const __nv_bfloat16*)base, base_gate, (__nv_bfloat16*)out, hidden);

@@ -653,6 +653,42 @@ __global__ void residual_conv_kernel(const T* __restrict__ x, int x_stride, int 
     out[(size_t)t * out_stride + c] = from_float<T>(to_float(x[(size_t)t * x_stride + c]) + acc);
 }
 
+// The same for bfloat16 rows that are whole 16-byte pieces: a thread takes eight neighbouring channels of a token.
+__global__ void residual_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, int channels, const float* __restrict__ weight, int taps,
+                                            const float* __restrict__ state, size_t slot_stride, int state_off, const int* __restrict__ slots,
+                                            const int* __restrict__ token_row, const int* __restrict__ row_start, __nv_bfloat16* __restrict__ out, int out_stride,
+                                            int first_token) {
+    const int t = first_token + blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= channels) return;
+    const int r = token_row[t];
+    const int i = t - row_start[r];
+    const float* kept = state + (size_t)slots[r] * slot_stride + state_off;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, now[8];
+    for (int j = taps - 1; j >= 0; --j) {  // oldest input first
+        float v[8];
+        if (i - j >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t - j) * x_stride + c);
+            const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(in[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+        } else {
+            const float* p = kept + (size_t)(taps - 1 + i - j) * channels + c;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = p[k];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            acc[k] = fmaf(weight[(size_t)(c + k) * taps + taps - 1 - j], v[k], acc[k]);
+            if (j == 0) now[k] = v[k];
+        }
+    }
+    uint4 packed;
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(now[2 * k] + acc[2 * k], now[2 * k + 1] + acc[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * out_stride + c) = packed;
+}
+
 template <typename T>
 __global__ void conv_state_keep_kernel(const T* __restrict__ x, int x_stride, int channels, int taps, float* __restrict__ state, size_t slot_stride,
                                        int state_off, const int* __restrict__ slots, const int* __restrict__ row_start, int rows) {
@@ -679,8 +715,15 @@ HB_EXPORT int hb_residual_conv(const void* x, int is_bf16, int x_stride, int cha
                                int out_stride, int tokens, cudaStream_t stream) {
     if (tokens <= 0 || channels <= 0) return 0;
     if (taps < 1) return HB_BAD_ARGUMENT;
+    const bool by_eight = is_bf16 && channels % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
     for (int first = 0; first < tokens; first += 65535) {
         const int count = tokens - first < 65535 ? tokens - first : 65535;
+        if (by_eight) {
+            residual_conv_bf16x8_kernel<<<dim3((channels / 8 + 127) / 128, count), 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, weight, taps, state,
+                                                                                                   (size_t)slot_stride, state_off, slots, token_row, row_start,
+                                                                                                   (__nv_bfloat16*)out, out_stride, first);
+            continue;
+        }
         const dim3 grid((channels + 255) / 256, count);
         if (is_bf16)
             residual_conv_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, weight, taps, state, (size_t)slot_stride, state_off, slots,

@@ -285,14 +285,19 @@ def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_he
                        k_norm: torch.Tensor | None = None, norm_whole: bool = False, eps: float = 0.0, inv_freq: torch.Tensor | None = None,
                        rot_dims: int = 0, rot_half: bool = False, k_scale: float = 1.0, cache: torch.Tensor | None = None,
                        block_table: torch.Tensor | None = None, token_row: torch.Tensor | None = None, page_size: int = 0,
-                       v_unit_eps: float | None = None, q_head_scale: torch.Tensor | None = None) -> None:
+                       v_unit_eps: float | None = None, q_head_scale: torch.Tensor | None = None, v_inv_freq: torch.Tensor | None = None,
+                       v_rot_dims: int = 0, v_rot_half: bool = False) -> None:
     """Float projections ``x`` [tokens, *] with queries at column ``q_off``, keys at ``k_off``, values at ``v_off``: query/key
     norm (per head with one weight, or over the whole projection with a weight per column), rotation (adjacent pairs, or
     dimension i with i + rot_dims / 2), keys times ``k_scale``; queries to ``q_out`` [tokens, >= q_heads * head_dim], keys and
     values into ``cache`` (either arrangement of :func:`paged_strides`) or keys to ``k_out`` (values then stay where they are).
     ``q_out`` and ``k_out`` may be float views of ``x`` itself.  ``v_unit_eps`` (with a cache): every value head is divided by
-    sqrt(mean(v^2) + v_unit_eps) before it is stored.  ``q_head_scale`` [q_heads] float: a factor on every query head, after norm and rotation."""
-    require_cuda(x, positions, q_out, k_out, q_norm, k_norm, inv_freq, cache, block_table, token_row, q_head_scale)
+    sqrt(mean(v^2) + v_unit_eps) before it is stored.  ``q_head_scale`` [q_heads] float: a factor on every query head, after norm and rotation.
+    ``v_inv_freq`` (with a cache): every value head is stored turned by its token's position over its first ``v_rot_dims`` entries (pairs as
+    ``v_rot_half`` says, pair i by position * v_inv_freq[i])."""
+    require_cuda(x, positions, q_out, k_out, q_norm, k_norm, inv_freq, cache, block_table, token_row, q_head_scale, v_inv_freq)
+    if v_inv_freq is not None and (v_inv_freq.dtype != torch.float32 or not v_inv_freq.is_contiguous() or v_inv_freq.numel() < v_rot_dims // 2 or cache is None):
+        raise KernelError("heads_prepare_wide: the values' frequencies are dense float32, one per rotated pair, and go with a cache")
     if q_head_scale is not None and (q_head_scale.dtype != torch.float32 or q_head_scale.numel() != q_heads or not q_head_scale.is_contiguous()):
         raise KernelError("heads_prepare_wide: the queries' factors are a dense float32 vector with one entry per head")
     if x.dtype != torch.float32 or x.stride(-1) != 1 or q_out.stride(-1) != 1 or (k_out is not None and (k_out.stride(-1) != 1 or k_out.dtype != q_out.dtype)):
@@ -315,7 +320,8 @@ def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_he
         i32(1 if rot_half else 0), ptr(positions), f32(k_scale), ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
         i32(k_out.stride(0) if k_out is not None else 0), i32(is_bf16(q_out)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
         ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1] if block_table is not None else 0),
-        ptr(token_row), i32(page_size), i32(pages), f32(-1.0 if v_unit_eps is None else v_unit_eps), ptr(q_head_scale), ptr(status_word(x.device)), stream_ptr()),
+        ptr(token_row), i32(page_size), i32(pages), f32(-1.0 if v_unit_eps is None else v_unit_eps), ptr(q_head_scale), ptr(v_inv_freq),
+        i32(v_rot_dims if v_inv_freq is not None else 0), i32(1 if v_rot_half else 0), ptr(status_word(x.device)), stream_ptr()),
         "heads_prepare_wide")
 
 
@@ -396,12 +402,15 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, slope: float) -> torch.Tens
 
 
 def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor | None, eps_post: float, offset: torch.Tensor | None,
-                  w_next: torch.Tensor | None, eps_next: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor | None:
+                  w_next: torch.Tensor | None, eps_next: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+                  gate: torch.Tensor | None = None) -> torch.Tensor | None:
     """One launch per sublayer boundary of a block that normalises what a sublayer reads *and* what it returns:
     ``h += y / rms(y) * w_post (+ offset)`` in the float stream, then ``h / rms(h) * w_next`` returned in ``out_dtype``.
     Without ``y`` only the offset is added; without ``w_next`` nothing is returned; with ``rows`` (int32 indices) only
-    those rows are worked on and ``h`` stays as it was."""
-    require_cuda(h, y, w_post, offset, w_next, rows)
+    those rows are worked on and ``h`` stays as it was.  ``gate`` [tokens, hidden] float: ``y`` is first multiplied, entry by entry, by sigmoid(gate)."""
+    require_cuda(h, y, w_post, offset, w_next, rows, gate)
+    if gate is not None and (y is None or gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape != h.shape or gate.stride(1) != 1):
+        raise KernelError("norm_add_norm: the gate is a float32 matrix of the stream's shape beside a sublayer output")
     if h.dtype != torch.float32 or not h.is_contiguous() or h.dim() != 2:
         raise KernelError("norm_add_norm: a dense float32 stream")
     tokens, hidden = h.shape
@@ -414,7 +423,7 @@ def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor 
     out = torch.empty((n_rows, hidden), dtype=out_dtype, device=h.device) if w_next is not None else None
     check(library("elementwise").hb_norm_add_norm(ptr(h), ptr(y), i32(is_bf16(y) if y is not None else 0), ptr(w_post), ptr(offset), ptr(w_next), ptr(out),
                                                   i32(is_bf16(out) if out is not None else 0), ptr(rows), i32(n_rows), i32(hidden), f32(eps_post),
-                                                  f32(eps_next), stream_ptr()), "norm_add_norm")
+                                                  f32(eps_next), ptr(gate), i32(gate.stride(0) if gate is not None else 0), stream_ptr()), "norm_add_norm")
     return out
 
 

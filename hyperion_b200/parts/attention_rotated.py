@@ -33,6 +33,7 @@ from .base import POSITIONS, BuildContext, Mixer, PagedKV, PagedTokens, WeightSp
 from .spec import PartSpec
 
 DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o"}
+LARGEST_HEAD = 640  # csrc/attention_generic.cu
 
 
 def _common_dtype(tensors) -> torch.dtype:
@@ -55,8 +56,8 @@ class RotatedValueAttention(GroupedQueryAttention):
         self.names = {**DEFAULT_NAMES, **dict(p.get("names") or {})}
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.kv_heads} key/value heads do not divide {self.heads} heads")
-        if max(self.head_dim, self.value_dim) > 256:
-            raise ValueError(f"heads of {self.head_dim} / {self.value_dim} are above the kernels' limit of 256")
+        if max(self.head_dim, self.value_dim) > LARGEST_HEAD:
+            raise ValueError(f"heads of {self.head_dim} / {self.value_dim} are above the kernel's limit of {LARGEST_HEAD}")
         self.position = make(POSITIONS, p["position"], build) if p.get("position") is not None else None
         self.value_position = make(POSITIONS, p["value_position"], build) if p.get("value_position") is not None else None
         for part, size in ((self.position, self.head_dim), (self.value_position, self.value_dim)):
@@ -111,14 +112,13 @@ class RotatedValueAttention(GroupedQueryAttention):
             raise ValueError("this attention writes a paged cache of its own; the schedule gave it none")
         proj = ops.linear(x, self.w_qkv, self.b_qkv, torch.float32)
         k_off, v_off = self.q_width, self.q_width + self.k_width
-        if self.value_position is not None:  # a value is cached turned by its own position
-            self._turn_values(proj, v_off, self.kv_heads, step.positions, 1.0)
         q = torch.empty((x.shape[0], self.q_width), dtype=self.dtype, device=x.device)
-        part = self.position
+        part, turned = self.position, self.value_position
         ops.heads_prepare_wide(proj, 0, k_off, v_off, self.heads, self.kv_heads, self.head_dim, self.value_dim, step.positions, q_out=q,
                                inv_freq=part.inv_freq if part is not None else None, rot_dims=part.dims if part is not None else 0,
                                rot_half=bool(getattr(part, "half", False)), cache=cache.kv, block_table=cache.block_table, token_row=step.token_row,
-                               page_size=cache.page_size)
+                               page_size=cache.page_size, v_inv_freq=turned.inv_freq if turned is not None else None,  # a value is cached turned by its own position
+                               v_rot_dims=turned.dims if turned is not None else 0, v_rot_half=bool(getattr(turned, "half", False)))
         if self.fast:
             attn = self._attend_fast(q, step, cache)
         else:

@@ -24,6 +24,28 @@ from .spec import PartSpec
 
 
 @dataclass
+class GatedResult:
+    """What a sublayer returned together with the pre-activations ``gate`` [tokens, hidden] (float) of a gate on it: whoever reads it
+    multiplies ``y``, entry by entry, by sigmoid(gate).  A norm that normalises a sublayer's output does so in its own launch
+    (``ops.norm_add_norm``); any other reader calls :meth:`tensor`."""
+
+    y: object  # a tensor, or a product still in its split-K pieces
+    gate: torch.Tensor
+
+    def tensor(self) -> torch.Tensor:
+        y = self.y.tensor() if hasattr(self.y, "tensor") else self.y
+        ops.sigmoid_gate_(y, self.gate, 0)
+        return y
+
+
+def _ungated(y):
+    """(the sublayer's output as a tensor, its gate or None)"""
+    if isinstance(y, GatedResult):
+        return (y.y.tensor() if hasattr(y.y, "tensor") else y.y), y.gate
+    return (y.tensor() if hasattr(y, "tensor") else y), None
+
+
+@dataclass
 class NormedDelta:
     """What a sublayer returned, still to be normalised by ``norm`` (an :class:`RMSNorm`) before it is added to the stream,
     plus a vector ``offset`` that is added to every row after it.  Either may be absent.  The next norm that reads the stream
@@ -35,8 +57,8 @@ class NormedDelta:
 
     def apply(self, h: torch.Tensor) -> None:
         """Do it now, for a reader of the stream that is not a norm."""
-        y = self.y.tensor() if hasattr(self.y, "tensor") else self.y
-        ops.norm_add_norm(h, y, self.norm.weight if y is not None else None, self.norm.eps if y is not None else 0.0, self.offset, None, 0.0, h.dtype)
+        y, gate = _ungated(self.y)
+        ops.norm_add_norm(h, y, self.norm.weight if y is not None else None, self.norm.eps if y is not None else 0.0, self.offset, None, 0.0, h.dtype, gate=gate)
 
 
 @dataclass
@@ -93,6 +115,8 @@ class RMSNorm(Norm):
         return [("elementwise", {})]
 
     def forward(self, h, delta, rows=None):
+        if isinstance(delta, GatedResult):  # a gated result that no norm stands on: multiplied here, added below
+            delta = delta.tensor()
         if self.groups > 1 or isinstance(delta, SumOfTwo):
             if isinstance(delta, NormedDelta):
                 delta.apply(h)
@@ -102,9 +126,9 @@ class RMSNorm(Norm):
                 first, second = first.float(), second.float()
             return ops.add_group_rmsnorm(h, first, second, self.weight, self.groups, self.eps, self.dtype, rows)
         if isinstance(delta, NormedDelta):
-            y = delta.y.tensor() if hasattr(delta.y, "tensor") else delta.y
+            y, gate = _ungated(delta.y)
             return ops.norm_add_norm(h, y, delta.norm.weight if y is not None else None, delta.norm.eps if y is not None else 0.0, delta.offset,
-                                     self.weight, self.eps, self.dtype, rows)
+                                     self.weight, self.eps, self.dtype, rows, gate=gate)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.dtype, rows)
 
     def add_normed(self, h, y):

@@ -9,7 +9,8 @@ the wrapper asks for that record *and* for whatever the inner mixer asks for.  P
 ``weight_name`` (a tensor [hidden_size, taps]), ``inner`` (a PartSpec).
 
 ``gated_output`` (mixer) and ``gated_feed_forward``: the inner part's result is multiplied, element by element, by
-sigmoid(W x + b) of the rows x that the wrapper itself was handed (the gate's product is kept in float).  Parameters:
+sigmoid(W x + b) of the rows x that the wrapper itself was handed (the gate's product is kept in float; it travels beside the
+result as a ``GatedResult``, so that a norm on the sublayer's output multiplies, normalises and adds in one launch).  Parameters:
 ``hidden_size``, ``weight_name``, ``bias_name``, ``inner`` (a PartSpec).
 """
 from __future__ import annotations
@@ -21,6 +22,7 @@ import torch
 from .. import ops
 from ..ops import recurrent
 from .base import FEED_FORWARDS, MIXERS, BuildContext, FeedForward, Mixer, RequestState, WeightSpec, make, register_feed_forward, register_mixer
+from .norm import GatedResult
 from .spec import PartSpec
 
 
@@ -88,11 +90,10 @@ def _gate_weights(part) -> dict[str, WeightSpec]:
     return {part.weight_name: WeightSpec((part.hidden, part.hidden)), part.bias_name: WeightSpec((part.hidden,))}
 
 
-def _gated(part, x: torch.Tensor, y) -> torch.Tensor:
-    gate = ops.linear(x, part.w_gate, part.b_gate, torch.float32)
-    y = y.tensor() if hasattr(y, "tensor") else y
-    ops.sigmoid_gate_(y, gate, 0)
-    return y
+def _gated(part, x: torch.Tensor, y) -> GatedResult:
+    """The inner part's result with the gate's pre-activations beside it: the norm that reads the result applies the gate in its own
+    launch; any other reader multiplies when it asks for the tensor."""
+    return GatedResult(y, ops.linear(x, part.w_gate, part.b_gate, torch.float32))
 
 
 class GatedMixer(_Wrapper, Mixer):

@@ -6,7 +6,7 @@ another layer's tensors, and greedy generation through ``Engine.generate``.
 
 The configurations and weights are made here.  Weights are drawn so that a fault shows: matrices of N(0, gain^2 / in) make the
 attention peaked, the router's matrices are four times as large again so that few choices are close calls, corrections are as large as
-many scores' differences so that choice and weight part ways, decays are spread over their useful range, and where a test is about one key a marker token, whose key points where the
+many scores' differences so that choice and weight part ways (in the two whole models they are whole numbers that settle the choice alone), decays are spread over their useful range, and where a test is about one key a marker token, whose key points where the
 last query points, makes that key's score stand out.  float32 runs are held to 3e-4 of the largest logit, which no wrong key,
 window or lost state survives; bfloat16 runs to 5e-2 of a row's root-mean-square logit.
 """
@@ -124,9 +124,11 @@ ALONE = {
 }
 
 
-def make_weights(doc: dict, seed: int, gain: float = 1.5) -> dict[str, torch.Tensor]:
+def make_weights(doc: dict, seed: int, gain: float = 1.5, decided: bool = False) -> dict[str, torch.Tensor]:
     """bfloat16 tensors under the design's names: matrices N(0, gain^2 / in), norm weights around 1, biases and the router's correction
-    of the size of what they are added to, decay rates spread over their useful range."""
+    of the size of what they are added to, decay rates spread over their useful range.  ``decided``: the corrections are whole numbers, all
+    different, so that they alone settle which experts are chosen (scores lie between 0 and 1) while the weights still follow the scores: a
+    model of several layers in bfloat16 then sends every token where exact arithmetic sends it, and can be held to it row by row."""
     from hyperion_b200.models import DecoderModel, get_architecture
 
     entry = get_architecture("Tobadra")
@@ -138,6 +140,8 @@ def make_weights(doc: dict, seed: int, gain: float = 1.5) -> dict[str, torch.Ten
         last = name.rsplit(".", 1)[-1]
         if last in ("norm", "norm1", "norm2", "norm1b", "norm2b"):
             t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif last == "correction" and decided:
+            t = torch.randperm(shape[0], generator=g).float()
         elif last == "correction":
             t = 0.15 * torch.randn(shape, generator=g)
         elif last == "router":  # decided scores: few tokens whose best experts lie so close that a rounding upstream swaps them
@@ -184,7 +188,7 @@ def folders(tmp_path_factory):
         folder = root / name
         folder.mkdir()
         (folder / "config.json").write_text(json.dumps(doc))
-        weights = make_weights(doc, 23 + index, gain=1.2 if name in CONFIGS else 1.5)
+        weights = make_weights(doc, 23 + index, gain=1.2 if name in CONFIGS else 1.5, decided=name in CONFIGS)
         if name in ("attention", "attention_64"):
             align_keys_with_queries(doc, weights)
             # the marker's pull must not be averaged away by what the convolution adds from the tokens before
@@ -239,15 +243,17 @@ def has_experts(doc: dict) -> bool:
     return any(entry["mlp"] is not None and entry["mlp"]["kind"] == "moe" for entry in doc["layers"])
 
 
-def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what=None, routed: bool = False) -> None:
-    """``routed``: in bfloat16 a token whose best experts lie close together may go to another expert than in exact arithmetic, and what
-    it then writes into a recurrence's state or a window's keys stays with the tokens after it: up to a fifth of the rows may be off,
-    while the middle row stays within half the tolerance (a fault of a kernel, a cache or a state moves every row)."""
-    if routed and dtype == "bfloat16":
+def assert_close(got: np.ndarray, want: np.ndarray, dtype: str, what=None, routed: bool = False, deep: bool = False) -> None:
+    """``routed`` (a layer whose router follows its input): in bfloat16 a token whose best experts lie close together may go to another
+    expert than in exact arithmetic, and what it then writes into a recurrence's state stays with the tokens after it: up to a fifth of the
+    rows may be off.  ``deep`` (a model of several layers, its routers decided by their corrections): roundings pass through six or seven
+    layers whose norms blow up what a small sublayer output carries: three rows in a hundred may be off.  Either way the middle row stays
+    within half the tolerance (a fault of a kernel, a cache or a state moves every row).  float32 is held to its line without exceptions."""
+    if (routed or deep) and dtype == "bfloat16":
         got2, want2 = np.atleast_2d(got), np.atleast_2d(want)
         errors = np.sqrt(((got2 - want2) ** 2).mean(axis=1)) / np.sqrt((want2 ** 2).mean(axis=1))
         over, middle = float((errors > TOLERANCE[dtype]).mean()), float(np.median(errors))
-        assert over <= 0.2 and middle <= TOLERANCE[dtype] / 2, (what, over, middle)
+        assert over <= (0.2 if routed else 0.03) and middle <= TOLERANCE[dtype] / 2, (what, over, middle)
         return
     error = relative_error(got, want)
     assert error <= TOLERANCE[dtype], (what, error)
@@ -344,7 +350,7 @@ def test_prefill_against_token_by_token_and_portions(folders, name, dtype):
     results = {"whole": run_cut(engine, "w", ids, [len(ids)]), "single": run_cut(engine, "s", ids, [1]),
                "pairs": run_cut(engine, "p", ids, [2]), "mixed sizes": run_cut(engine, "m", ids, [7, 2, 16, 3, 33, 1, 1, 64])}
     for how, got in results.items():
-        assert_close(got, want, dtype, how, routed=True)
+        assert_close(got, want, dtype, how, deep=True)
         assert rows_over(got, results["whole"], TOLERANCE[dtype]) <= 0.1, how  # the same arithmetic on both sides
         if dtype == "float32":
             assert np.array_equal(got, results["whole"]), how  # float32: the same bits however the work is cut
@@ -392,7 +398,7 @@ def test_unequal_requests_together_over_pages_and_slots_that_are_used_again(fold
         step += 1
     engine.check()
     engine.cache.check()
-    assert_close(np.concatenate(got_rows), np.concatenate(want_rows), dtype, routed=True)
+    assert_close(np.concatenate(got_rows), np.concatenate(want_rows), dtype, deep=True)
     assert max(len(users) for users in slots_seen.values()) >= 2  # a slot served more than one request
 
 
@@ -501,7 +507,7 @@ def test_first_tokens_and_long_decoding(folders, name, dtype):
     engine.finish("pair")
     engine.check()
     single = np.stack(rows)
-    assert_close(single, want, dtype, routed=True)
+    assert_close(single, want, dtype, deep=True)
     assert_close(single[:8], want[:8], dtype, "the first tokens")
     assert_close(pair, want[:2], dtype)
     whole = run_cut(engine, "whole", ids, [len(ids)])
@@ -604,7 +610,7 @@ def test_replay_through_the_command(folders, dtype, tmp_path):
     expected = {0: [ref["a"][39], ref["b"][0], ref["b"][30]], 1: [ref["a"][40], ref["a"][41], ref["b"][31]], 2: [ref["b"][32]],
                 3: [ref["c"][49], ref["a"][69]]}
     for step, rows in expected.items():
-        assert_close(read(step), np.stack(rows), dtype, step, routed=True)
+        assert_close(read(step), np.stack(rows), dtype, step)
 
 
 def test_the_command_line_writes_a_random_model_and_generates_with_it(tmp_path):
