@@ -908,13 +908,18 @@ def tobadra_kernels(size: dict, measured: dict) -> dict:
         heads, kv_heads, dim, _, rot = size["attention"]
         proj = torch.randn(tokens, (heads + 2 * kv_heads) * dim, device=dev)
         freq_v, freq_qk = torch.rand(dim // 2, device=dev), torch.rand(rot // 2, device=dev)
-        report(f"rotate_values/{shape}", timed(lambda: ops.rotate_heads_(proj, (heads + kv_heads) * dim, kv_heads, dim, positions, freq_v, dim, True, 1.0)), tokens * kv_heads * dim * 8)
+        page, context = 16, before + max(counts)
+        per_row = -(-context // page)
+        table = torch.arange(rows * per_row, dtype=torch.int32, device=dev).view(rows, per_row)
+        cache = torch.zeros(rows * per_row, 2, kv_heads, page, dim, dtype=torch.bfloat16, device=dev)
+        q = torch.empty(tokens, heads * dim, dtype=torch.bfloat16, device=dev)
+        prepare = lambda turned: ops.heads_prepare_wide(proj, 0, heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim, dim, positions, q_out=q, inv_freq=freq_qk, rot_dims=rot,
+                                                        rot_half=True, cache=cache, block_table=table, token_row=token_row, page_size=page,
+                                                        v_inv_freq=freq_v if turned else None, v_rot_dims=dim if turned else 0, v_rot_half=True)
+        report(f"attention.prepare_with_turned_values/{shape}", timed(lambda: prepare(True)), tokens * (heads + 2 * kv_heads) * dim * 6)
+        report(f"mirovik.attention_prepare/{shape}", timed(lambda: prepare(False)), tokens * (heads + 2 * kv_heads) * dim * 6)
         attn = torch.randn(tokens, heads * dim, device=dev).to(torch.bfloat16)
         report(f"rotate_result_back/{shape}", timed(lambda: ops.rotate_heads_(attn, 0, heads, dim, positions, freq_v, dim, True, -1.0)), tokens * heads * dim * 4)
-        q = torch.empty(tokens, heads * dim, dtype=torch.bfloat16, device=dev)
-        k = torch.empty(tokens, kv_heads * dim, dtype=torch.bfloat16, device=dev)
-        report(f"mirovik.rotate_q_k/{shape}", timed(lambda: ops.heads_prepare_wide(proj, 0, heads * dim, (heads + kv_heads) * dim, heads, kv_heads, dim, dim, positions, q_out=q, k_out=k,
-                                                                                inv_freq=freq_qk, rot_dims=rot, rot_half=True)), tokens * (heads + kv_heads) * dim * 6)
         # the two recurrences and their gated norms; the like kernels: the delta rule with one decay per head, the same scan as retention
         d_heads, n, e, rank = size["delta"]
         conv = torch.randn(tokens, 2 * d_heads * n + d_heads * e, device=dev) * 0.5
@@ -945,7 +950,8 @@ def tobadra_kernels(size: dict, measured: dict) -> dict:
         if cut is not None:  # the long row in segments side by side, as the bfloat16 engine walks it
             seg_start, seg_row = torch.tensor(cut[0], dtype=torch.int32, device=dev), torch.tensor(cut[1], dtype=torch.int32, device=dev)
             report(f"lightning.scan_in_segments/{shape}", timed(lambda: recurrent.retention_in_segments(qkv, l_heads * ln, 0, 2 * l_heads * ln, l_decay, l_state, slots, seg_start, seg_row,
-                                                                                                         len(cut[1]), l_heads, ln, ln, le)), l_bytes, fp32_flops=8.0 * tokens * l_heads * ln * le)
+                                                                                                         len(cut[1]), l_heads, ln, ln, le)), l_bytes,
+                   fp32_flops=8.0 * tokens * l_heads * ln * le)
         lo = torch.randn(tokens, l_heads * le, device=dev)
         report(f"lightning.gated_norm_over_all_heads/{shape}", timed(lambda: recurrent.gated_group_norm(lo, qkv, 2 * l_heads * ln + l_heads * le, norm_all[: l_heads * le], l_heads * le, False,
                                                                                                      1e-6, torch.bfloat16, sigmoid_gate=True)), tokens * l_heads * le * 10)

@@ -633,7 +633,8 @@ HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gat
 // out[t, c] = x[t, c] + sum_j weight[c, j] * x[t - (taps - 1 - j), c] over the tokens of t's own request (the last column of the weight
 // multiplies the current token); inputs before the row's first token come from the request's state (its last taps - 1 inputs as floats,
 // oldest first; zero for a new request).  Rows and result share an element type; the sum is float, rounded once.
-// hb_conv_state_keep then stores every row's last taps - 1 inputs for the next step.  silu_columns: silu in place over some columns of float rows.
+// hb_conv_state_keep then stores every row's last taps - 1 inputs for the next step.  silu_columns: silu in place over some columns of float rows
+// (a recurrence whose keys, queries and values are activated projections; taken inside the scan's preparation it cost more than this pass).
 namespace {
 template <typename T>
 __global__ void residual_conv_kernel(const T* __restrict__ x, int x_stride, int channels, const float* __restrict__ weight, int taps,
@@ -653,7 +654,9 @@ __global__ void residual_conv_kernel(const T* __restrict__ x, int x_stride, int 
     out[(size_t)t * out_stride + c] = from_float<T>(to_float(x[(size_t)t * x_stride + c]) + acc);
 }
 
-// The same for bfloat16 rows that are whole 16-byte pieces: a thread takes eight neighbouring channels of a token.
+// The same for bfloat16 rows that are whole 16-byte pieces: a thread takes eight neighbouring channels of a token; their 8 * TAPS weights lie
+// side by side and are read in 16-byte pieces.
+template <int TAPS>
 __global__ void residual_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, int channels, const float* __restrict__ weight, int taps,
                                             const float* __restrict__ state, size_t slot_stride, int state_off, const int* __restrict__ slots,
                                             const int* __restrict__ token_row, const int* __restrict__ row_start, __nv_bfloat16* __restrict__ out, int out_stride,
@@ -664,7 +667,14 @@ __global__ void residual_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x,
     const int i = t - row_start[r];
     const float* kept = state + (size_t)slots[r] * slot_stride + state_off;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, now[8];
-    for (int j = taps - 1; j >= 0; --j) {  // oldest input first
+    float w[8 * TAPS];
+#pragma unroll
+    for (int k = 0; k < 2 * TAPS; ++k) {
+        const float4 piece = *reinterpret_cast<const float4*>(weight + (size_t)c * TAPS + 4 * k);
+        w[4 * k] = piece.x; w[4 * k + 1] = piece.y; w[4 * k + 2] = piece.z; w[4 * k + 3] = piece.w;
+    }
+#pragma unroll
+    for (int j = TAPS - 1; j >= 0; --j) {  // oldest input first
         float v[8];
         if (i - j >= 0) {
             const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t - j) * x_stride + c);
@@ -672,13 +682,13 @@ __global__ void residual_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x,
 #pragma unroll
             for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(in[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
         } else {
-            const float* p = kept + (size_t)(taps - 1 + i - j) * channels + c;
+            const float* p = kept + (size_t)(TAPS - 1 + i - j) * channels + c;
 #pragma unroll
             for (int k = 0; k < 8; ++k) v[k] = p[k];
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            acc[k] = fmaf(weight[(size_t)(c + k) * taps + taps - 1 - j], v[k], acc[k]);
+            acc[k] = fmaf(w[k * TAPS + TAPS - 1 - j], v[k], acc[k]);
             if (j == 0) now[k] = v[k];
         }
     }
@@ -687,6 +697,13 @@ __global__ void residual_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ x,
 #pragma unroll
     for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(now[2 * k] + acc[2 * k], now[2 * k + 1] + acc[2 * k + 1]);
     *reinterpret_cast<uint4*>(out + (size_t)t * out_stride + c) = packed;
+}
+
+__global__ void silu_columns_kernel(float* __restrict__ x, int x_stride, int col0, int columns, long long count) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        float* p = x + (size_t)(i / columns) * x_stride + col0 + (int)(i % columns);
+        *p = silu_f(*p);
+    }
 }
 
 template <typename T>
@@ -701,13 +718,6 @@ __global__ void conv_state_keep_kernel(const T* __restrict__ x, int x_stride, in
         kept[(size_t)s * channels + c] = src >= 0 ? to_float(x[(size_t)(first + src) * x_stride + c]) : kept[(size_t)(s + n) * channels + c];
     }
 }
-
-__global__ void silu_columns_kernel(float* __restrict__ x, int x_stride, int col0, int columns, long long count) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
-        float* p = x + (size_t)(i / columns) * x_stride + col0 + (int)(i % columns);
-        *p = silu_f(*p);
-    }
-}
 }  // namespace
 
 HB_EXPORT int hb_residual_conv(const void* x, int is_bf16, int x_stride, int channels, const float* weight, int taps, const float* state,
@@ -715,13 +725,19 @@ HB_EXPORT int hb_residual_conv(const void* x, int is_bf16, int x_stride, int cha
                                int out_stride, int tokens, cudaStream_t stream) {
     if (tokens <= 0 || channels <= 0) return 0;
     if (taps < 1) return HB_BAD_ARGUMENT;
-    const bool by_eight = is_bf16 && channels % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+    const bool by_eight = is_bf16 && taps <= 8 && channels % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 &&
+                          (((uintptr_t)x | (uintptr_t)out | (uintptr_t)weight) & 15) == 0;
     for (int first = 0; first < tokens; first += 65535) {
         const int count = tokens - first < 65535 ? tokens - first : 65535;
         if (by_eight) {
-            residual_conv_bf16x8_kernel<<<dim3((channels / 8 + 127) / 128, count), 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, weight, taps, state,
-                                                                                                   (size_t)slot_stride, state_off, slots, token_row, row_start,
-                                                                                                   (__nv_bfloat16*)out, out_stride, first);
+            const dim3 eights((channels / 8 + 127) / 128, count);
+#define HB_CONV8(T)                                                                                                                                       \
+    case T:                                                                                                                                               \
+        residual_conv_bf16x8_kernel<T><<<eights, 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, weight, taps, state, (size_t)slot_stride, \
+                                                                   state_off, slots, token_row, row_start, (__nv_bfloat16*)out, out_stride, first);      \
+        break
+            switch (taps) { HB_CONV8(1); HB_CONV8(2); HB_CONV8(3); HB_CONV8(4); HB_CONV8(5); HB_CONV8(6); HB_CONV8(7); HB_CONV8(8); }
+#undef HB_CONV8
             continue;
         }
         const dim3 grid((channels + 255) / 256, count);
@@ -735,6 +751,13 @@ HB_EXPORT int hb_residual_conv(const void* x, int is_bf16, int x_stride, int cha
     return launch_status();
 }
 
+HB_EXPORT int hb_silu_columns(float* x, int x_stride, int col0, int columns, int tokens, cudaStream_t stream) {
+    if (tokens <= 0 || columns <= 0) return 0;
+    const long long count = (long long)tokens * columns, wanted = (count + 255) / 256;
+    silu_columns_kernel<<<(int)(wanted < 4096 ? wanted : 4096), 256, 0, stream>>>(x, x_stride, col0, columns, count);
+    return launch_status();
+}
+
 HB_EXPORT int hb_conv_state_keep(const void* x, int is_bf16, int x_stride, int channels, int taps, float* state, long long slot_stride, int state_off,
                                  const int* slots, const int* row_start, int rows, cudaStream_t stream) {
     if (rows <= 0 || channels <= 0 || taps <= 1) return 0;
@@ -742,13 +765,6 @@ HB_EXPORT int hb_conv_state_keep(const void* x, int is_bf16, int x_stride, int c
     const dim3 grid((channels + 127) / 128, rows);
     if (is_bf16) conv_state_keep_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, channels, taps, state, (size_t)slot_stride, state_off, slots, row_start, rows);
     else conv_state_keep_kernel<<<grid, 128, 0, stream>>>((const float*)x, x_stride, channels, taps, state, (size_t)slot_stride, state_off, slots, row_start, rows);
-    return launch_status();
-}
-
-HB_EXPORT int hb_silu_columns(float* x, int x_stride, int col0, int columns, int tokens, cudaStream_t stream) {
-    if (tokens <= 0 || columns <= 0) return 0;
-    const long long count = (long long)tokens * columns, wanted = (count + 255) / 256;
-    silu_columns_kernel<<<(int)(wanted < 4096 ? wanted : 4096), 256, 0, stream>>>(x, x_stride, col0, columns, count);
     return launch_status();
 }
 
