@@ -618,7 +618,7 @@ HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gat
                                                                     eps, scale, (float*)out, out_stride, sigmoid_gate);
         return launch_status();
     }
-    const int threads = 256;
+    const int threads = group >= 4096 ? 1024 : (group >= 2048 ? 512 : 256);  // a wide group (one norm over all heads): fewer trips per thread
     const dim3 grid(tokens, groups);
     if (out_is_bf16)
         gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps, scale,

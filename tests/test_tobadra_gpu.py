@@ -111,9 +111,9 @@ ALONE = {
     "attention_128": document(64, 61, [layer(attention(6, 2, 128, 128, 0.08, window=100, rot=128))], taps=0),
     "attention_open": document(40, 61, [layer(attention(3, 3, 8, 12, 0.6, rot=4))], taps=1),
     "lightning": document(48, 97, [layer(lightning(3, 12, 20, [0.5, 0.97, 1.0]))], taps=4),
-    "lightning_wide": document(40, 61, [layer(lightning(1, 136, 72, [0.99]))], taps=2),
+    "lightning_wide": document(40, 61, [layer(lightning(1, 132, 72, [0.99]))], taps=2),
     "channel_delta": document(48, 97, [layer(channel_delta(4, 2, 12, 20, 4, decay_rank=6, gate_rank=5))], taps=3),
-    "channel_delta_wide": document(40, 61, [layer(channel_delta(1, 1, 136, 24, 1, decay_rank=3, gate_rank=2))], taps=2),
+    "channel_delta_wide": document(40, 61, [layer(channel_delta(1, 1, 132, 24, 1, decay_rank=3, gate_rank=2))], taps=2),
     # (a state of 8 x 8: with fewer entries a head's output is a sum of so few products that it cancels now and then, and the norms after it
     # blow a rounding up into a difference)
     "dense": document(48, 97, [layer(lightning(2, 8, 8, [0.5, 0.9]), dense(100))], taps=2),
