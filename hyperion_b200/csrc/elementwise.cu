@@ -672,14 +672,15 @@ HB_EXPORT int hb_stream_copy(const float* h, void* copy, long long count, cudaSt
 // sublayer boundary:   h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w_post (+ offset);   out[i] = h[t] / sqrt(mean(h[t]^2) + eps) * w_next.
 // Every piece is optional: without y only the offset is added, without w_next nothing is normalised for a reader.  With `rows`
 // only the listed rows are worked on and h is left as it was (the last norm of a model, where only some rows are read).
-// With `gate` [tokens, gate_stride] (float) the sublayer's output is first multiplied, entry by entry, by sigmoid(gate[t]): a block whose
-// sublayers are gated by a projection of what they read hands the projection on instead of launching the product itself.
+// With `gate` [tokens, gate_stride] (float) the sublayer's output is first multiplied, entry by entry, by sigmoid(gate[t] + gate_bias): a block whose
+// sublayers are gated by a projection of what they read hands the projection on instead of launching the product itself.  The projection may
+// still lie in `gate_splits` split-K pieces, `gate_split_stride` floats apart, which are added up here in split order, after the bias.
 // Everything is float; sums of squares are taken in a fixed order per row.
 template <typename TY, typename TO>
 __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict__ y, const float* __restrict__ w_post,
                                      const float* __restrict__ offset, const float* __restrict__ w_next, TO* __restrict__ out,
                                      const int* __restrict__ rows, int hidden, float eps_post, float eps_next, const float* __restrict__ gate,
-                                     int gate_stride) {
+                                     int gate_stride, int gate_splits, size_t gate_split_stride, const float* __restrict__ gate_bias) {
     extern __shared__ float row_values[];
     __shared__ float scratch[32];
     const int i = blockIdx.x, t = rows ? rows[i] : i;
@@ -691,7 +692,13 @@ __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict
         float sum = 0.f;
         for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
             float v = to_float(yrow[j]);
-            if (grow) v *= 1.0f / (1.0f + expf(-grow[j]));
+            if (grow) {
+                float g = gate_bias ? gate_bias[j] : 0.f;
+                for (int piece = 0; piece < gate_splits; ++piece) g += grow[(size_t)piece * gate_split_stride + j];
+                const float open = 1.0f / (1.0f + expf(-g));
+                v *= open;
+                row_values[j] = open;  // kept for the second pass over the row
+            }
             sum = fmaf(v, v, sum);
         }
         inv_y = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + eps_post);
@@ -699,7 +706,7 @@ __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict
     float sum = 0.f;
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         float v = hrow[j];
-        if (yrow) v += to_float(yrow[j]) * (grow ? 1.0f / (1.0f + expf(-grow[j])) : 1.f) * inv_y * w_post[j];
+        if (yrow) v += to_float(yrow[j]) * (grow ? row_values[j] : 1.f) * inv_y * w_post[j];
         if (offset) v += offset[j];
         row_values[j] = v;
         if (!rows) hrow[j] = v;
@@ -715,7 +722,7 @@ __global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict
 __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, const float* __restrict__ w_post,
                                             const float* __restrict__ offset, const float* __restrict__ w_next, __nv_bfloat16* __restrict__ out,
                                             const int* __restrict__ rows, int hidden, float eps_post, float eps_next, const float* __restrict__ gate,
-                                            int gate_stride) {
+                                            int gate_stride, int gate_splits, size_t gate_split_stride, const float* __restrict__ gate_bias) {
     __shared__ float scratch[32];
     const int i = blockIdx.x, t = rows ? rows[i] : i, j = threadIdx.x * 8;
     const bool active = j < hidden;
@@ -731,9 +738,16 @@ __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bf
                 v[2 * k] = f.x; v[2 * k + 1] = f.y;
             }
             if (gate) {
-                const float* grow = gate + (size_t)t * gate_stride + j;
-                const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
-                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (gate_bias) {
+                    const float4 b0 = *reinterpret_cast<const float4*>(gate_bias + j), b1 = *reinterpret_cast<const float4*>(gate_bias + j + 4);
+                    g[0] = b0.x; g[1] = b0.y; g[2] = b0.z; g[3] = b0.w; g[4] = b1.x; g[5] = b1.y; g[6] = b1.z; g[7] = b1.w;
+                }
+                for (int piece = 0; piece < gate_splits; ++piece) {
+                    const float* grow = gate + (size_t)piece * gate_split_stride + (size_t)t * gate_stride + j;
+                    const float4 g0 = *reinterpret_cast<const float4*>(grow), g1 = *reinterpret_cast<const float4*>(grow + 4);
+                    g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
+                }
 #pragma unroll
                 for (int k = 0; k < 8; ++k) v[k] *= 1.0f / (1.0f + expf(-g[k]));
             }
@@ -781,15 +795,15 @@ __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bf
 
 HB_EXPORT int hb_norm_add_norm(float* h, const void* y, int y_is_bf16, const float* w_post, const float* offset, const float* w_next, void* out,
                                int out_is_bf16, const int* rows, int n_rows, int hidden, float eps_post, float eps_next, const float* gate,
-                               int gate_stride, cudaStream_t stream) {
+                               int gate_stride, int gate_splits, long long gate_split_stride, const float* gate_bias, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (hidden <= 0 || hidden > 49152 || (y && !w_post) || (w_next && !out)) return HB_BAD_ARGUMENT;
+    if (hidden <= 0 || hidden > 49152 || (y && !w_post) || (w_next && !out) || (gate && gate_splits < 1)) return HB_BAD_ARGUMENT;
     const bool halves = (!y || y_is_bf16) && (!w_next || out_is_bf16);
-    if (halves && hidden % 8 == 0 && hidden <= 8192 && (!gate || gate_stride % 4 == 0) &&
-        (((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)offset | (uintptr_t)w_next | (uintptr_t)out | (uintptr_t)gate) & 15) == 0) {
+    if (halves && hidden % 8 == 0 && hidden <= 8192 && (!gate || (gate_stride % 4 == 0 && gate_split_stride % 4 == 0)) &&
+        (((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)offset | (uintptr_t)w_next | (uintptr_t)out | (uintptr_t)gate | (uintptr_t)gate_bias) & 15) == 0) {
         const int lanes = ((hidden / 8 + 31) / 32) * 32;  // which kernel runs follows from the width and the types alone
         norm_add_norm_bf16x8_kernel<<<n_rows, lanes, 0, stream>>>(h, (const __nv_bfloat16*)y, w_post, offset, w_next, (__nv_bfloat16*)out, rows, hidden,
-                                                                  eps_post, eps_next, gate, gate_stride);
+                                                                  eps_post, eps_next, gate, gate_stride, gate_splits, (size_t)gate_split_stride, gate_bias);
         return launch_status();
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -798,7 +812,8 @@ HB_EXPORT int hb_norm_add_norm(float* h, const void* y, int y_is_bf16, const flo
     do {                                                                                                                                  \
         if (shared > 48 * 1024) cudaFuncSetAttribute(norm_add_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared); \
         norm_add_norm_kernel<TY, TO><<<n_rows, threads, shared, stream>>>(h, (const TY*)y, w_post, offset, w_next, (TO*)out, rows, hidden,   \
-                                                                         eps_post, eps_next, gate, gate_stride);                         \
+                                                                         eps_post, eps_next, gate, gate_stride, gate_splits,            \
+                                                                         (size_t)gate_split_stride, gate_bias);                          \
     } while (0)
     const bool y16 = y && y_is_bf16, o16 = w_next && out_is_bf16;
     if (y16 && o16) HB_NORM_ADD_NORM(__nv_bfloat16, __nv_bfloat16);

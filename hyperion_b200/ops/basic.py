@@ -403,14 +403,26 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, slope: float) -> torch.Tens
 
 def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor | None, eps_post: float, offset: torch.Tensor | None,
                   w_next: torch.Tensor | None, eps_next: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None,
-                  gate: torch.Tensor | None = None) -> torch.Tensor | None:
+                  gate=None, gate_bias: torch.Tensor | None = None) -> torch.Tensor | None:
     """One launch per sublayer boundary of a block that normalises what a sublayer reads *and* what it returns:
     ``h += y / rms(y) * w_post (+ offset)`` in the float stream, then ``h / rms(h) * w_next`` returned in ``out_dtype``.
     Without ``y`` only the offset is added; without ``w_next`` nothing is returned; with ``rows`` (int32 indices) only
-    those rows are worked on and ``h`` stays as it was.  ``gate`` [tokens, hidden] float: ``y`` is first multiplied, entry by entry, by sigmoid(gate)."""
-    require_cuda(h, y, w_post, offset, w_next, rows, gate)
+    those rows are worked on and ``h`` stays as it was.  ``gate`` [tokens, hidden] float, or a product still in its split-K pieces
+    (``ops.gemm.SplitSum`` without a bias of its own), and ``gate_bias`` [hidden] float: ``y`` is first multiplied, entry by entry, by
+    sigmoid(gate + gate_bias)."""
+    from .gemm import SplitSum
+
+    gate_splits, gate_split_stride = 1, 0
+    if isinstance(gate, SplitSum):
+        if gate.bias is not None or not gate.partials.is_contiguous():
+            raise KernelError("norm_add_norm: a gate in split-K pieces comes dense and without a bias of its own")
+        pieces = gate.partials
+        gate_splits, gate_split_stride, gate = pieces.shape[0], pieces.shape[1] * pieces.shape[2], pieces[0]
+    require_cuda(h, y, w_post, offset, w_next, rows, gate, gate_bias)
     if gate is not None and (y is None or gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape != h.shape or gate.stride(1) != 1):
         raise KernelError("norm_add_norm: the gate is a float32 matrix of the stream's shape beside a sublayer output")
+    if gate_bias is not None and (gate is None or gate_bias.dtype != torch.float32 or gate_bias.numel() != h.shape[1] or not gate_bias.is_contiguous()):
+        raise KernelError("norm_add_norm: the gate's bias is a dense float32 vector of the stream's width beside a gate")
     if h.dtype != torch.float32 or not h.is_contiguous() or h.dim() != 2:
         raise KernelError("norm_add_norm: a dense float32 stream")
     tokens, hidden = h.shape
@@ -423,7 +435,8 @@ def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor 
     out = torch.empty((n_rows, hidden), dtype=out_dtype, device=h.device) if w_next is not None else None
     check(library("elementwise").hb_norm_add_norm(ptr(h), ptr(y), i32(is_bf16(y) if y is not None else 0), ptr(w_post), ptr(offset), ptr(w_next), ptr(out),
                                                   i32(is_bf16(out) if out is not None else 0), ptr(rows), i32(n_rows), i32(hidden), f32(eps_post),
-                                                  f32(eps_next), ptr(gate), i32(gate.stride(0) if gate is not None else 0), stream_ptr()), "norm_add_norm")
+                                                  f32(eps_next), ptr(gate), i32(gate.stride(0) if gate is not None else 0), i32(gate_splits),
+                                                  ctypes.c_longlong(gate_split_stride), ptr(gate_bias), stream_ptr()), "norm_add_norm")
     return out
 
 

@@ -59,8 +59,8 @@ def _takes_own_kernel(x: torch.Tensor, weight: torch.Tensor, bias, out_dtype) ->
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, may_leave_partials: bool = False):
-    """``may_leave_partials``: the caller's result is only ever a residual delta, so a product that was split over K may
-    come back as a :class:`hyperion_b200.ops.gemm.SplitSum` (the norm that adds the delta reads the pieces itself)."""
+    """``may_leave_partials``: the caller's result has one reader that can add up split-K pieces itself (a residual delta, a gate that
+    the next norm applies), so a product that was split over K may come back as a :class:`hyperion_b200.ops.gemm.SplitSum`."""
     require_cuda(x, weight, bias)
     out_dtype = out_dtype or x.dtype
     if weight.dtype == torch.float32:
@@ -75,7 +75,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         epilogue = gemm.EPI_F32 if out_dtype == torch.float32 else gemm.EPI_BF16
         if xin.shape[0] > gemm.PAIR_MIN_ROWS:  # only under HYPERION_B200_GEMM=own: prompt-sized products on pairs of SMs
             return gemm.gemm_pair_bf16(xin, weight, bias, epilogue)
-        return gemm.gemm_bf16(xin, weight, bias, epilogue, leave_partials=may_leave_partials and out_dtype == torch.bfloat16)
+        return gemm.gemm_bf16(xin, weight, bias, epilogue, leave_partials=may_leave_partials)
     if not xin.is_contiguous():
         xin = xin.contiguous()
     if out_dtype == torch.bfloat16:

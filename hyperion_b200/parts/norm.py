@@ -25,24 +25,29 @@ from .spec import PartSpec
 
 @dataclass
 class GatedResult:
-    """What a sublayer returned together with the pre-activations ``gate`` [tokens, hidden] (float) of a gate on it: whoever reads it
-    multiplies ``y``, entry by entry, by sigmoid(gate).  A norm that normalises a sublayer's output does so in its own launch
-    (``ops.norm_add_norm``); any other reader calls :meth:`tensor`."""
+    """What a sublayer returned together with the pre-activations of a gate on it: ``gate`` [tokens, hidden] float (a tensor, or a product
+    still in its split-K pieces) plus the vector ``bias``.  Whoever reads it multiplies ``y``, entry by entry, by sigmoid(gate + bias).  A
+    norm that normalises a sublayer's output does so in its own launch (``ops.norm_add_norm``, which also adds up the pieces and the bias);
+    any other reader calls :meth:`tensor`."""
 
     y: object  # a tensor, or a product still in its split-K pieces
-    gate: torch.Tensor
+    gate: object
+    bias: Optional[torch.Tensor] = None
 
     def tensor(self) -> torch.Tensor:
         y = self.y.tensor() if hasattr(self.y, "tensor") else self.y
-        ops.sigmoid_gate_(y, self.gate, 0)
+        gate = self.gate.tensor() if hasattr(self.gate, "tensor") else self.gate
+        if self.bias is not None:
+            gate = gate + self.bias
+        ops.sigmoid_gate_(y, gate, 0)
         return y
 
 
 def _ungated(y):
-    """(the sublayer's output as a tensor, its gate or None)"""
+    """(the sublayer's output as a tensor, its gate or None, the gate's bias or None)"""
     if isinstance(y, GatedResult):
-        return (y.y.tensor() if hasattr(y.y, "tensor") else y.y), y.gate
-    return (y.tensor() if hasattr(y, "tensor") else y), None
+        return (y.y.tensor() if hasattr(y.y, "tensor") else y.y), y.gate, y.bias
+    return (y.tensor() if hasattr(y, "tensor") else y), None, None
 
 
 @dataclass
@@ -57,8 +62,9 @@ class NormedDelta:
 
     def apply(self, h: torch.Tensor) -> None:
         """Do it now, for a reader of the stream that is not a norm."""
-        y, gate = _ungated(self.y)
-        ops.norm_add_norm(h, y, self.norm.weight if y is not None else None, self.norm.eps if y is not None else 0.0, self.offset, None, 0.0, h.dtype, gate=gate)
+        y, gate, gate_bias = _ungated(self.y)
+        ops.norm_add_norm(h, y, self.norm.weight if y is not None else None, self.norm.eps if y is not None else 0.0, self.offset, None, 0.0, h.dtype, gate=gate,
+                          gate_bias=gate_bias)
 
 
 @dataclass
@@ -126,9 +132,9 @@ class RMSNorm(Norm):
                 first, second = first.float(), second.float()
             return ops.add_group_rmsnorm(h, first, second, self.weight, self.groups, self.eps, self.dtype, rows)
         if isinstance(delta, NormedDelta):
-            y, gate = _ungated(delta.y)
+            y, gate, gate_bias = _ungated(delta.y)
             return ops.norm_add_norm(h, y, delta.norm.weight if y is not None else None, delta.norm.eps if y is not None else 0.0, delta.offset,
-                                     self.weight, self.eps, self.dtype, rows, gate=gate)
+                                     self.weight, self.eps, self.dtype, rows, gate=gate, gate_bias=gate_bias)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.dtype, rows)
 
     def add_normed(self, h, y):

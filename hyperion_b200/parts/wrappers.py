@@ -93,7 +93,7 @@ def _gate_weights(part) -> dict[str, WeightSpec]:
 def _gated(part, x: torch.Tensor, y) -> GatedResult:
     """The inner part's result with the gate's pre-activations beside it: the norm that reads the result applies the gate in its own
     launch; any other reader multiplies when it asks for the tensor."""
-    return GatedResult(y, ops.linear(x, part.w_gate, part.b_gate, torch.float32))
+    return GatedResult(y, ops.linear(x, part.w_gate, None, torch.float32, may_leave_partials=True), part.b_gate)
 
 
 class GatedMixer(_Wrapper, Mixer):
@@ -108,7 +108,7 @@ class GatedMixer(_Wrapper, Mixer):
         return {**_gate_weights(self), **self._inner_weights()}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.w_gate, self.b_gate = tensors[self.weight_name].contiguous(), tensors[self.bias_name].contiguous()
+        self.w_gate, self.b_gate = tensors[self.weight_name].contiguous(), tensors[self.bias_name].to(torch.float32).contiguous()
         self._load_inner(tensors)
 
     def cache_request(self):
@@ -133,7 +133,7 @@ class GatedFeedForward(_Wrapper, FeedForward):
         return {**_gate_weights(self), **self._inner_weights()}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.w_gate, self.b_gate = tensors[self.weight_name].contiguous(), tensors[self.bias_name].contiguous()
+        self.w_gate, self.b_gate = tensors[self.weight_name].contiguous(), tensors[self.bias_name].to(torch.float32).contiguous()
         self._load_inner(tensors)
 
     def kernel_modules(self):
