@@ -126,7 +126,7 @@ ALONE = {
 
 def make_weights(doc: dict, seed: int, gain: float = 1.5, decided: bool = False) -> dict[str, torch.Tensor]:
     """bfloat16 tensors under the design's names: matrices N(0, gain^2 / in), norm weights around 1, biases and the router's correction
-    of the size of what they are added to, decay rates spread over their useful range.  ``decided``: the corrections are whole numbers, all
+    of the size of what they are added to, decay rates spread over their useful range.  ``decided``: the corrections are even whole numbers, all
     different, so that they alone settle which experts are chosen (scores lie between 0 and 1) while the weights still follow the scores: a
     model of several layers in bfloat16 then sends every token where exact arithmetic sends it, and can be held to it row by row."""
     from hyperion_b200.models import DecoderModel, get_architecture
@@ -141,7 +141,7 @@ def make_weights(doc: dict, seed: int, gain: float = 1.5, decided: bool = False)
         if last in ("norm", "norm1", "norm2", "norm1b", "norm2b"):
             t = 1.0 + 0.2 * torch.randn(shape, generator=g)
         elif last == "correction" and decided:
-            t = torch.randperm(shape[0], generator=g).float()
+            t = 2.0 * torch.randperm(shape[0], generator=g).float()  # steps of two: a score of exactly one beside one of zero is no tie
         elif last == "correction":
             t = 0.15 * torch.randn(shape, generator=g)
         elif last == "router":  # decided scores: few tokens whose best experts lie so close that a rounding upstream swaps them
@@ -632,3 +632,84 @@ def test_the_command_line_writes_a_random_model_and_generates_with_it(tmp_path):
     for _ in range(5):
         ids.append(int(plain.forward(plain_config, weights, ids)[-1].argmax()))
     assert got["tokens"] == ids[len(prompt):] and got["finish_reason"] == "length"
+
+
+# ------------------------------------------------------------------------------------------ configurations drawn at random
+def _random_document(seed: int) -> dict:
+    """A model whose every size, option and constant is drawn: widths, heads and groupings, head sizes that the tensor-core kernels take and
+    others, windows, rotations, taps, experts with or without identities, groups and a shared expert, layers without a feed-forward, layers
+    that borrow tensors, in any order."""
+    import random
+
+    r = random.Random(seed)
+    width = r.choice([32, 40, 56, 64, 80, 128])
+
+    def feed_forward():
+        kind = r.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            return None
+        if kind == "dense":
+            return dense(r.choice([24, 50, 96]))
+        experts, identity = r.randint(1, 7), r.randint(0, 3)
+        outputs = experts + identity
+        count = r.choice([c for c in range(1, outputs + 1) if outputs % c == 0])
+        keep = r.randint(1, count)
+        top = r.randint(1, min(4, keep * (outputs // count)))
+        groups = (count, keep) if r.random() < 0.8 else None
+        if groups is None:
+            top = r.randint(1, min(4, outputs))
+        return moe(r.choice([8, 20, 40]), experts, top, r.choice([0.5, 1.0, 2.5]), identity=identity, groups=groups, shared=r.choice([None, 16, 24]))
+
+    def mixer():
+        kind = r.choice(["attention", "attention", "lightning", "channel_delta"])
+        if kind == "attention":
+            kv = r.choice([1, 2, 3])
+            heads = kv * r.choice([1, 2, 3])
+            dim = r.choice([8, 16, 24, 32, 40, 64])
+            vdim = r.choice([dim, dim, 12, 20, 32])
+            rot = r.choice([None, dim, r.randrange(2, dim + 1, 2)])
+            return attention(heads, kv, dim, vdim, r.choice([0.1, 0.2, dim ** -0.5]), window=r.choice([None, r.randint(2, 70)]), rot=rot, base=r.choice([100.0, 10000.0, 1e6]))
+        if kind == "lightning":
+            heads = r.randint(1, 3)
+            return lightning(heads, r.choice([8, 12, 32]), r.choice([8, 20, 32]), [r.choice([0.5, 0.9, 0.99, 1.0]) for _ in range(heads)])
+        kv = r.choice([1, 2])
+        return channel_delta(kv * r.choice([1, 2]), kv, r.choice([8, 12, 32]), r.choice([8, 20]), r.randint(1, 4), decay_rank=r.randint(1, 6), gate_rank=r.randint(1, 6))
+
+    layers = [layer(mixer(), feed_forward()) for _ in range(r.randint(2, 4))]
+    for _ in range(r.randint(0, 2)):
+        layers.insert(r.randint(1, len(layers)), None)  # a place for a layer that borrows
+    filled = []  # a borrowing layer may stand before or after the layer it borrows from
+    for i, entry in enumerate(layers):
+        if entry is None:
+            source = r.choice([j for j in range(len(layers)) if layers[j] is not None])
+            filled.append({**layers[source], "weights_of": source})
+        else:
+            filled.append(entry)
+    return document(width, r.randint(40, 300), filled, taps=r.choice([0, 1, 2, 4, 5]), eps=r.choice([1e-6, 1e-5, 1e-3]), logit_scale=r.choice([0.5, 1.0, 3.0]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Eight models drawn at random, in float32 against the plain implementation: a whole prompt, the same in portions, and two requests of
+    unequal progress side by side; in bfloat16 the middle row of the whole prompt."""
+    from hyperion_b200.engine.batch import StepEntry
+    from hyperion_b200.weights import write_file
+
+    doc = _random_document(seed)
+    folder = tmp_path / "model"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(doc))
+    write_file(folder / "model.safetensors", make_weights(doc, 100 + seed, gain=1.2, decided=True))
+    ids, other = ids_for(seed, 90, doc["vocab"]), ids_for(seed + 50, 37, doc["vocab"])
+    want, want_other = plain_logits(folder, ids), plain_logits(folder, other)
+    engine = engine_for(folder, "float32", page_size=8, max_tokens=512)
+    assert_close(run_cut(engine, "w", ids, [len(ids)]), want, "float32", ("whole", doc))
+    assert_close(run_cut(engine, "p", ids, [3, 1, 2, 17]), want, "float32", ("portions", doc))
+    engine.step([StepEntry("a", ids[:61], []), StepEntry("b", other[:5], [])])
+    got = engine.step([StepEntry("a", [ids[61]], [0]), StepEntry("b", other[5:], list(range(32)))]).cpu().numpy()
+    engine.check()
+    assert_close(got, np.concatenate([want[61:62], want_other[5:]]), "float32", ("side by side", doc))
+    engine = engine_for(folder, "bfloat16", page_size=8, max_tokens=512)
+    got = run_cut(engine, "w", ids, [len(ids)])
+    errors = np.sqrt(((got - want) ** 2).mean(axis=1)) / np.sqrt((want ** 2).mean(axis=1))
+    assert np.median(errors) <= TOLERANCE["bfloat16"], (float(np.median(errors)), doc)
