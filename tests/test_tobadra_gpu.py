@@ -713,3 +713,30 @@ def test_configurations_drawn_at_random(seed, tmp_path):
     got = run_cut(engine, "w", ids, [len(ids)])
     errors = np.sqrt(((got - want) ** 2).mean(axis=1)) / np.sqrt((want ** 2).mean(axis=1))
     assert np.median(errors) <= TOLERANCE["bfloat16"], (float(np.median(errors)), doc)
+
+
+def test_sizes_of_one_and_many_groups(tmp_path):
+    """Every size that can be one is one (heads, key and value sizes of one and two, a window of one position, one tap, one expert, as many
+    choices as router outputs, inner sizes of one), and a router of 36 outputs in 12 groups with eight query heads on one key/value head and
+    seven taps: whole, in portions and token by token, in both precisions."""
+    from hyperion_b200.weights import write_file
+
+    docs = {
+        "ones": document(8, 17, [layer(attention(1, 1, 2, 2, 1.0, window=1, rot=2), moe(4, 1, 1, 1.0)),
+                                 layer(lightning(1, 1, 1, [1.0]), moe(4, 1, 2, 3.0, identity=1, groups=(2, 2), shared=4)),
+                                 layer(channel_delta(1, 1, 1, 1, 1, decay_rank=1, gate_rank=1), dense(1)),
+                                 layer(attention(1, 1, 4, 2, 0.5, window=2, rot=2))], taps=1, eps=1e-6),
+        "many": document(24, 50, [layer(attention(8, 1, 16, 16, 0.25, window=33, rot=16), moe(8, 30, 6, 2.0, identity=6, groups=(12, 5), shared=8)),
+                                  layer(channel_delta(6, 3, 16, 16, 4, decay_rank=2, gate_rank=2), moe(8, 9, 8, 1.0, groups=(3, 3)))], taps=7),
+    }
+    for name, doc in docs.items():
+        folder = tmp_path / name
+        folder.mkdir()
+        (folder / "config.json").write_text(json.dumps(doc))
+        write_file(folder / "model.safetensors", make_weights(doc, 7, gain=1.2, decided=True))
+        ids = ids_for(1, 90, doc["vocab"])
+        want = plain_logits(folder, ids)
+        for dtype in ("float32", "bfloat16"):
+            engine = engine_for(folder, dtype, page_size=8, max_tokens=512)
+            for sizes in ([len(ids)], [3, 1, 2, 17], [1]):
+                assert_close(run_cut(engine, "w", ids, sizes), want, dtype, (name, sizes), deep=True)
